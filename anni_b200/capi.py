@@ -1,0 +1,92 @@
+"""ctypes binding of ``libanni_b200.so`` -- the only way Python reaches the kernels.
+
+Loading fails loudly when the library is missing or cannot be built: there is no
+Python or CPU implementation of the step to fall back on.
+"""
+import ctypes as C
+import os
+
+from . import build as _build
+
+_LIB = None
+
+DT_F32, DT_BF16 = 0, 1
+SEG_WD, SEG_TWIN_BF16, SEG_TWIN_FP8 = 1, 2, 4
+STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE = 1, 2, 4
+OK, E_ARG, E_CUDA, E_BARRIER_TIMEOUT, E_NOMEM, E_LIMIT = 0, -1, -2, -3, -4, -5
+
+
+class Config(C.Structure):
+    _fields_ = [("n_arena", C.c_uint64), ("shard_off", C.c_uint64), ("shard_n", C.c_uint64),
+                ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("n_seg", C.c_int),
+                ("seg_off", C.c_void_p), ("seg_flags", C.c_void_p)]
+
+
+class Buffers(C.Structure):
+    _fields_ = [("master", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p),
+                ("grad", C.c_void_p), ("twin_bf16", C.c_void_p), ("twin_fp8", C.c_void_p)]
+
+
+class Hyper(C.Structure):
+    _fields_ = [("lr", C.c_double), ("beta1", C.c_double), ("beta2", C.c_double),
+                ("eps", C.c_double), ("weight_decay", C.c_double), ("grad_clip", C.c_double),
+                ("grad_scale", C.c_double), ("t", C.c_int), ("flags", C.c_int)]
+
+
+class Status(C.Structure):
+    _fields_ = [("sumsq", C.c_double), ("norm", C.c_double), ("eff_scale", C.c_double),
+                ("loss_scale", C.c_double), ("skipped", C.c_int32), ("error", C.c_int32),
+                ("good_steps", C.c_int32), ("steps_done", C.c_int32)]
+
+
+def lib():
+    """The loaded library (built on first use when nvcc is available)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.LIB
+    if not os.path.exists(path) or (_build.needs_build() and _build.shutil.which("nvcc")):
+        path = _build.build()
+    L = C.CDLL(path, mode=C.RTLD_GLOBAL)
+    vp, i, d = C.c_void_p, C.c_int, C.c_double
+    L.anni_optstep_create.restype = i
+    L.anni_optstep_create.argtypes = [C.POINTER(Config), C.POINTER(vp)]
+    L.anni_optstep_destroy.restype = None
+    L.anni_optstep_destroy.argtypes = [vp]
+    L.anni_optstep_bind.restype = i
+    L.anni_optstep_bind.argtypes = [vp, C.POINTER(Buffers)]
+    for name in ("anni_optstep_step", "anni_optstep_norm", "anni_optstep_update"):
+        f = getattr(L, name)
+        f.restype = i
+        f.argtypes = [vp, C.POINTER(Hyper), vp]
+    L.anni_optstep_quantize.restype = i
+    L.anni_optstep_quantize.argtypes = [vp, vp]
+    for name in ("anni_optstep_reduce_buffer", "anni_optstep_amax_buffer",
+                 "anni_optstep_scale_buffer"):
+        f = getattr(L, name)
+        f.restype = vp
+        f.argtypes = [vp]
+    L.anni_optstep_status_read.restype = i
+    L.anni_optstep_status_read.argtypes = [vp, C.POINTER(Status), vp]
+    L.anni_optstep_loss_scale_init.restype = i
+    L.anni_optstep_loss_scale_init.argtypes = [vp, d, i, d, d, d, d]
+    L.anni_optstep_grid.restype = i
+    L.anni_optstep_grid.argtypes = [vp, C.POINTER(i), C.POINTER(i)]
+    L.anni_kernel_launches.restype = C.c_uint64
+    L.anni_kernel_launches.argtypes = []
+    _LIB = L
+    return L
+
+
+class AnniError(RuntimeError):
+    def __init__(self, what, code):
+        names = {E_ARG: "bad argument", E_CUDA: "CUDA call failed",
+                 E_BARRIER_TIMEOUT: "bounded device wait timed out",
+                 E_NOMEM: "out of memory", E_LIMIT: "size beyond the stated maximum"}
+        super().__init__(f"{what}: {names.get(code, 'error')} ({code})")
+        self.code = code
+
+
+def check(what, code):
+    if code != OK:
+        raise AnniError(what, code)

@@ -1,0 +1,953 @@
+/*
+** Packed-arena optimizer step for B200 (sm_100a): the kernels and their launchers.
+**
+** The work is HBM-bound streaming arithmetic, so there are no tensor cores
+** here.  What the design spends its effort on instead:
+**   - every HBM access of the main path is a 128-bit coalesced load or store
+**     with a streaming cache hint, eight elements per thread per chunk;
+**   - the grid is persistent (a multiple of the SM count, all blocks
+**     co-resident) and every block owns one contiguous run of chunks, walked
+**     forwards for the norm and backwards for the update so that the tail of
+**     the gradient shard is still in L2 when it is read the second time;
+**   - the global dependency (the gradient norm) is resolved on the device:
+**     fixed-order fp64 block partials, a bounded device-wide barrier, and every
+**     block derives the same clip factor / skip decision from the same bits;
+**   - tensor boundaries, the decay mask and the twin format are looked up from
+**     a replicated segment table per chunk, so one launch covers every tensor.
+**
+** Arithmetic (what "parity" is measured against): the moments are updated in
+** double with the roundings of lang/lm_adam.c:587-591 of the reference
+** (products and sum rounded separately, result stored as float), which makes
+** m and v bit-identical to the reference's host loop whenever the gradient
+** multiplier is bit-identical.  The parameter update uses the float moments
+** with IEEE float division and square root; it stays within one ulp of the
+** reference's double expression for ordinary magnitudes.
+*/
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <atomic>
+#include "optstep_internal.h"
+
+namespace {
+
+/* ---- small device helpers ------------------------------------------------ */
+
+struct f32x8 {
+	float	x[ANNI_VEC];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
+{
+	uint32_t v;
+
+	asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+	return v;
+}
+
+__device__ __forceinline__ float sqrt_approx(float x)
+{
+	float r;
+
+	asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+	return r;
+}
+
+__device__ __forceinline__ float rcp_approx(float x)
+{
+	float r;
+
+	asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+	return r;
+}
+
+__device__ __forceinline__ f32x8 unpack_bf16x8(uint4 q)
+{
+	f32x8 r;
+
+	r.x[0] = __uint_as_float(q.x << 16);
+	r.x[1] = __uint_as_float(q.x & 0xffff0000u);
+	r.x[2] = __uint_as_float(q.y << 16);
+	r.x[3] = __uint_as_float(q.y & 0xffff0000u);
+	r.x[4] = __uint_as_float(q.z << 16);
+	r.x[5] = __uint_as_float(q.z & 0xffff0000u);
+	r.x[6] = __uint_as_float(q.w << 16);
+	r.x[7] = __uint_as_float(q.w & 0xffff0000u);
+	return r;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+	__nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);	/* round to nearest even */
+
+	return *reinterpret_cast<uint32_t *>(&h);
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const f32x8 &r)
+{
+	uint4 q;
+
+	q.x = pack_bf16x2(r.x[0], r.x[1]);
+	q.y = pack_bf16x2(r.x[2], r.x[3]);
+	q.z = pack_bf16x2(r.x[4], r.x[5]);
+	q.w = pack_bf16x2(r.x[6], r.x[7]);
+	return q;
+}
+
+/* eight consecutive elements starting at element index e of a typed buffer */
+template <typename T> struct io8;
+
+template <> struct io8<float> {
+	static __device__ __forceinline__ f32x8 load(const void *base, uint64_t e)
+	{
+		const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const float *>(base) + e);
+		uint4 a = __ldcs(p);
+		uint4 b = __ldcs(p + 1);
+		f32x8 r;
+
+		r.x[0] = __uint_as_float(a.x);
+		r.x[1] = __uint_as_float(a.y);
+		r.x[2] = __uint_as_float(a.z);
+		r.x[3] = __uint_as_float(a.w);
+		r.x[4] = __uint_as_float(b.x);
+		r.x[5] = __uint_as_float(b.y);
+		r.x[6] = __uint_as_float(b.z);
+		r.x[7] = __uint_as_float(b.w);
+		return r;
+	}
+	/* same, default cache policy: the norm phase wants its last reads to stay in L2 */
+	static __device__ __forceinline__ f32x8 load_keep(const void *base, uint64_t e)
+	{
+		const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const float *>(base) + e);
+		uint4 a = p[0];
+		uint4 b = p[1];
+		f32x8 r;
+
+		r.x[0] = __uint_as_float(a.x);
+		r.x[1] = __uint_as_float(a.y);
+		r.x[2] = __uint_as_float(a.z);
+		r.x[3] = __uint_as_float(a.w);
+		r.x[4] = __uint_as_float(b.x);
+		r.x[5] = __uint_as_float(b.y);
+		r.x[6] = __uint_as_float(b.z);
+		r.x[7] = __uint_as_float(b.w);
+		return r;
+	}
+	static __device__ __forceinline__ void store(void *base, uint64_t e, const f32x8 &r)
+	{
+		uint4 *p = reinterpret_cast<uint4 *>(static_cast<float *>(base) + e);
+
+		__stcs(p, make_uint4(__float_as_uint(r.x[0]), __float_as_uint(r.x[1]),
+		    __float_as_uint(r.x[2]), __float_as_uint(r.x[3])));
+		__stcs(p + 1, make_uint4(__float_as_uint(r.x[4]), __float_as_uint(r.x[5]),
+		    __float_as_uint(r.x[6]), __float_as_uint(r.x[7])));
+	}
+	static __device__ __forceinline__ void zero(void *base, uint64_t e)
+	{
+		uint4 *p = reinterpret_cast<uint4 *>(static_cast<float *>(base) + e);
+
+		__stcs(p, make_uint4(0, 0, 0, 0));
+		__stcs(p + 1, make_uint4(0, 0, 0, 0));
+	}
+	static __device__ __forceinline__ float load1(const void *base, uint64_t e)
+	{
+		return static_cast<const float *>(base)[e];
+	}
+	static __device__ __forceinline__ void store1(void *base, uint64_t e, float x)
+	{
+		static_cast<float *>(base)[e] = x;
+	}
+};
+
+template <> struct io8<__nv_bfloat16> {
+	static __device__ __forceinline__ f32x8 load(const void *base, uint64_t e)
+	{
+		return unpack_bf16x8(__ldcs(reinterpret_cast<const uint4 *>(
+		    static_cast<const uint16_t *>(base) + e)));
+	}
+	static __device__ __forceinline__ f32x8 load_keep(const void *base, uint64_t e)
+	{
+		return unpack_bf16x8(*reinterpret_cast<const uint4 *>(
+		    static_cast<const uint16_t *>(base) + e));
+	}
+	static __device__ __forceinline__ void store(void *base, uint64_t e, const f32x8 &r)
+	{
+		__stcs(reinterpret_cast<uint4 *>(static_cast<uint16_t *>(base) + e), pack_bf16x8(r));
+	}
+	static __device__ __forceinline__ void zero(void *base, uint64_t e)
+	{
+		__stcs(reinterpret_cast<uint4 *>(static_cast<uint16_t *>(base) + e),
+		    make_uint4(0, 0, 0, 0));
+	}
+	static __device__ __forceinline__ float load1(const void *base, uint64_t e)
+	{
+		return __uint_as_float((uint32_t)static_cast<const uint16_t *>(base)[e] << 16);
+	}
+	static __device__ __forceinline__ void store1(void *base, uint64_t e, float x)
+	{
+		__nv_bfloat16 h = __float2bfloat16_rn(x);
+
+		static_cast<uint16_t *>(base)[e] = *reinterpret_cast<uint16_t *>(&h);
+	}
+};
+
+/* largest s with seg_off[s] <= x (x inside [seg_off[0], seg_off[n_seg])) */
+__device__ __forceinline__ int seg_find(const int64_t *seg_off, int n_seg, int64_t x)
+{
+	int lo = 0;
+	int hi = n_seg - 1;
+
+	while (lo < hi) {
+		int mid = (lo + hi + 1) >> 1;
+
+		if (seg_off[mid] <= x)
+			lo = mid;
+		else
+			hi = mid - 1;
+	}
+	return lo;
+}
+
+/*
+** Which chunks a block owns.  Chunks are dealt out in "super-chunks" of
+** 2^sc_log2 consecutive chunks, round-robin over the grid: iteration `it` of
+** block b is chunk ((it >> sc) * grid + b) << sc | (it & mask).  At any moment
+** the whole grid then works inside one contiguous window of every buffer
+** (good DRAM page locality), while each block still streams runs of
+** 2^sc_log2 * ANNI_CHUNK consecutive elements.
+*/
+struct chunk_walk {
+	uint64_t	chunks;	/* chunks in the shard */
+	uint64_t	iters;	/* iterations of this block (some of the last may fall outside) */
+	uint32_t	sc;
+};
+
+__device__ __forceinline__ chunk_walk walk_init(uint64_t n, int sc_log2)
+{
+	chunk_walk w;
+	const uint64_t per_round = (uint64_t)gridDim.x << sc_log2;
+
+	w.chunks = (n + ANNI_CHUNK - 1) / ANNI_CHUNK;
+	w.sc = (uint32_t)sc_log2;
+	w.iters = ((w.chunks + per_round - 1) / per_round) << sc_log2;
+	return w;
+}
+
+/* chunk index of iteration `it`; >= w.chunks means "nothing there" */
+__device__ __forceinline__ uint64_t walk_chunk(const chunk_walk &w, uint64_t it)
+{
+	return ((((it >> w.sc) * gridDim.x + blockIdx.x) << w.sc) | (it & ((1u << w.sc) - 1u)));
+}
+
+__device__ __forceinline__ double warp_sum(double v)
+{
+#pragma unroll
+	for (int k = 16; k > 0; k >>= 1)
+		v += __shfl_down_sync(0xffffffffu, v, k);
+	return v;
+}
+
+/* Block sum in a fixed order; the result is valid in thread 0. */
+__device__ __forceinline__ double block_sum(double v)
+{
+	__shared__ double s_w[ANNI_THREADS / 32];
+	const int lane = threadIdx.x & 31;
+	const int w = threadIdx.x >> 5;
+
+	v = warp_sum(v);
+	if (lane == 0)
+		s_w[w] = v;
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		v = 0.0;
+#pragma unroll
+		for (int k = 0; k < ANNI_THREADS / 32; k++)
+			v += s_w[k];
+	}
+	return v;
+}
+
+/*
+** Device-wide barrier with a bounded wait.  All blocks of the grid are
+** co-resident (cooperative launch), so the wait ends as soon as the slowest
+** block arrives; the poll limit only matters if something is badly wrong, in
+** which case the block records the error and the kernel returns without
+** touching the parameters.  Returns false on timeout (uniform over the block).
+*/
+__device__ __forceinline__ bool grid_barrier(anni_control *ctl, uint32_t target)
+{
+	__shared__ int s_ok;
+
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		uint32_t polls = 0;
+		int ok = 1;
+
+		__threadfence();
+		atomicAdd(&ctl->bar_count, 1u);
+		while (ld_acquire_u32(&ctl->bar_count) < target) {
+			__nanosleep(32);
+			if (++polls > ANNI_WAIT_POLLS) {
+				ok = 0;
+				atomicExch(&ctl->error, ANNI_E_BARRIER_TIMEOUT);
+				break;
+			}
+		}
+		__threadfence();
+		s_ok = ok;
+	}
+	__syncthreads();
+	return s_ok != 0;
+}
+
+/* Sum of the block partials in index order; every thread of the block gets it. */
+__device__ __forceinline__ double sum_partials(const anni_control *ctl, int nparts)
+{
+	__shared__ double s_total;
+
+	if (threadIdx.x < 32) {
+		const volatile double *p = ctl->partials;
+		double v = 0.0;
+
+		for (int k = threadIdx.x; k < nparts; k += 32)
+			v += p[k];
+		v = warp_sum(v);
+		if (threadIdx.x == 0)
+			s_total = v;
+	}
+	__syncthreads();
+	return s_total;
+}
+
+/* ---- phase A: sum of squares of this block's chunks ---------------------- */
+
+template <typename GradT>
+__device__ __forceinline__ double norm_phase(const anni_launch &a, const chunk_walk &w)
+{
+	double acc0 = 0.0;
+	double acc1 = 0.0;
+	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+
+#pragma unroll 2
+	for (uint64_t it = 0; it < w.iters; it++) {
+		const uint64_t c = walk_chunk(w, it);
+		const uint64_t e = c * ANNI_CHUNK + t8;
+
+		if (c >= w.chunks)
+			continue;
+		if (a.aligned && e + ANNI_VEC <= a.n) {
+			f32x8 g = io8<GradT>::load_keep(a.grad, e);
+
+			/* squares and their sum in double: the skip decision and the clip
+			** factor then agree with a double accumulation to the last bits */
+#pragma unroll
+			for (int k = 0; k < ANNI_VEC; k += 2) {
+				const double g0 = (double)g.x[k];
+				const double g1 = (double)g.x[k + 1];
+
+				acc0 = fma(g0, g0, acc0);
+				acc1 = fma(g1, g1, acc1);
+			}
+		} else {
+			for (int k = 0; k < ANNI_VEC; k++)
+				if (e + k < a.n) {
+					double g = (double)io8<GradT>::load1(a.grad, e + k);
+
+					acc0 = fma(g, g, acc0);
+				}
+		}
+	}
+	return acc0 + acc1;
+}
+
+/* ---- the decision every block takes from the same bits --------------------- */
+
+struct decision {
+	double	coef;	/* multiplier of the raw gradient */
+	double	norm;
+	bool	skip;
+};
+
+__device__ __forceinline__ decision decide(const anni_launch &a, double ss, double nonfinite,
+	double loss_scale)
+{
+	decision d;
+	double gs = a.grad_scale;
+
+	if ((a.flags & ANNI_STEP_DEV_LOSS_SCALE) && loss_scale > 0.0)
+		gs = gs / loss_scale;
+	d.coef = gs;
+	d.norm = 0.0;
+	d.skip = false;
+	if (a.flags & ANNI_LAUNCH_NEED_NORM) {
+		d.norm = sqrt(ss) * fabs(gs);
+		if ((a.flags & ANNI_STEP_CHECK_FINITE) && (!isfinite(d.norm) || nonfinite > 0.0))
+			d.skip = true;
+		else if (a.clip > 0.0 && d.norm > a.clip)
+			d.coef = gs * (a.clip / (d.norm + 1e-12));
+	}
+	return d;
+}
+
+/* ---- phase B: AdamW on one element ----------------------------------------- */
+
+__device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, float lrwd,
+	float gf, float &p, float &m, float &v)
+{
+	/* moments: the reference's double expression, each product and the sum rounded on its own */
+	const double g = __dmul_rn((double)gf, coef);
+	const double md = __dadd_rn(__dmul_rn(a.b1, (double)m), __dmul_rn(a.omb1, g));
+	const double vd = __dadd_rn(__dmul_rn(a.b2, (double)v), __dmul_rn(__dmul_rn(a.omb2, g), g));
+
+	m = __double2float_rn(md);
+	v = __double2float_rn(vd);
+	/*
+	** p -= lr * (m/bc1) / (sqrt(v/bc2) + eps), then p -= lr*wd*p on the stored
+	** value.  The quotient uses the SFU square root and reciprocal (about one
+	** ulp each): the update term carries a relative error of a few 1e-7, which
+	** moves p by far less than one ulp unless p itself is of the size of the
+	** update.  Every product is rounded on its own (no contraction).
+	*/
+	const float den = __fadd_rn(sqrt_approx(__fmul_rn(v, a.ibc2)), a.eps);
+	const float upd = __fmul_rn(__fmul_rn(a.lrbc1, m), rcp_approx(den));
+
+	p = __fsub_rn(p, upd);
+	p = __fmaf_rn(-lrwd, p, p);
+}
+
+template <typename GradT, typename StateT>
+__device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t e, double coef,
+	uint32_t sflags, float &tmax)
+{
+	const float lrwd = (sflags & ANNI_SEG_WD) ? a.lrwd : 0.0f;
+	f32x8 g = io8<GradT>::load(a.grad, e);
+	f32x8 p = io8<float>::load(a.master, e);
+	f32x8 m = io8<StateT>::load(a.m, e);
+	f32x8 v = io8<StateT>::load(a.v, e);
+
+#pragma unroll
+	for (int k = 0; k < ANNI_VEC; k++)
+		adam_elem(a, coef, lrwd, g.x[k], p.x[k], m.x[k], v.x[k]);
+	io8<float>::store(a.master, e, p);
+	io8<StateT>::store(a.m, e, m);
+	io8<StateT>::store(a.v, e, v);
+	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16)
+		io8<__nv_bfloat16>::store(a.twin16, e, p);
+	if (sflags & ANNI_SEG_TWIN_FP8) {
+#pragma unroll
+		for (int k = 0; k < ANNI_VEC; k++)
+			tmax = fmaxf(tmax, fabsf(p.x[k]));
+	}
+	if (a.flags & ANNI_STEP_ZERO_GRAD)
+		io8<GradT>::zero(a.grad, e);
+}
+
+/* element-wise path for chunks that cross a tensor boundary, the arena end, or unaligned buffers */
+template <typename GradT, typename StateT>
+__device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64_t e, double coef,
+	bool skip)
+{
+	for (int k = 0; k < ANNI_VEC; k++) {
+		const uint64_t i = e + k;
+
+		if (i >= a.n)
+			break;
+		if (!skip) {
+			const int s = seg_find(a.seg_off, a.n_seg, (int64_t)(a.arena_off + i));
+			const uint32_t sflags = a.seg_flags[s];
+			const float lrwd = (sflags & ANNI_SEG_WD) ? a.lrwd : 0.0f;
+			float p = a.master[i];
+			float m = io8<StateT>::load1(a.m, i);
+			float v = io8<StateT>::load1(a.v, i);
+
+			adam_elem(a, coef, lrwd, io8<GradT>::load1(a.grad, i), p, m, v);
+			a.master[i] = p;
+			io8<StateT>::store1(a.m, i, m);
+			io8<StateT>::store1(a.v, i, v);
+			if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16)
+				io8<__nv_bfloat16>::store1(a.twin16, i, p);
+			if (sflags & ANNI_SEG_TWIN_FP8)
+				atomicMax(reinterpret_cast<int *>(&a.seg_amax[s]),
+				    __float_as_int(fabsf(p)));
+		}
+		if (a.flags & ANNI_STEP_ZERO_GRAD)
+			io8<GradT>::store1(a.grad, i, 0.0f);
+	}
+}
+
+__device__ __forceinline__ void amax_flush(const anni_launch &a, int seg, float &tmax)
+{
+	float w = tmax;
+
+#pragma unroll
+	for (int k = 16; k > 0; k >>= 1)
+		w = fmaxf(w, __shfl_xor_sync(0xffffffffu, w, k));
+	if ((threadIdx.x & 31) == 0 && w > 0.0f)
+		atomicMax(reinterpret_cast<int *>(&a.seg_amax[seg]), __float_as_int(w));
+	tmax = 0.0f;
+}
+
+template <typename GradT, typename StateT>
+__device__ __forceinline__ void update_phase(const anni_launch &a, const chunk_walk &w,
+	const decision &d)
+{
+	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	float tmax = 0.0f;
+	int seg = -1;
+	int amax_seg = -1;
+
+	if (d.skip && !(a.flags & ANNI_STEP_ZERO_GRAD))
+		return;
+	/* backwards: the chunks read last by the norm phase are the likeliest to sit in L2 */
+	for (uint64_t it = w.iters; it > 0; it--) {
+		const uint64_t c = walk_chunk(w, it - 1);
+		const uint64_t base = c * ANNI_CHUNK;
+		const int64_t abase = (int64_t)(a.arena_off + base);
+		bool whole;
+
+		if (c >= w.chunks)
+			continue;
+		if (seg < 0)
+			seg = seg_find(a.seg_off, a.n_seg, abase);
+		while (abase < a.seg_off[seg])
+			seg--;
+		whole = a.aligned && base + ANNI_CHUNK <= a.n
+		    && abase + ANNI_CHUNK <= a.seg_off[seg + 1];
+		if (whole && !d.skip) {
+			const uint32_t sflags = a.seg_flags[seg];
+
+			if (amax_seg != seg) {
+				if (amax_seg >= 0)
+					amax_flush(a, amax_seg, tmax);
+				amax_seg = (sflags & ANNI_SEG_TWIN_FP8) ? seg : -1;
+			}
+			update_chunk_vec<GradT, StateT>(a, base + t8, d.coef, sflags, tmax);
+		} else if (whole) {
+			io8<GradT>::zero(a.grad, base + t8);	/* skipped step: only the gradients change */
+		} else
+			update_chunk_scalar<GradT, StateT>(a, base + t8, d.coef, d.skip);
+	}
+	if (amax_seg >= 0)
+		amax_flush(a, amax_seg, tmax);
+}
+
+/* ---- phase C: e4m3 twins of the fresh master ------------------------------- */
+
+/* dequantisation scale of a tensor from its amax (num/gpu_cuda.cu:927-938 of the reference) */
+__device__ __forceinline__ float fp8_scale(float amax)
+{
+	float s = amax;
+
+	if (!(s > 0.0f) || !isfinite(s))
+		s = 1e-8f;
+	s = __fdiv_rn(s, 448.0f);
+	return s < 1e-12f ? 1e-12f : s;
+}
+
+__device__ __forceinline__ void quantize_phase(const anni_launch &a, const chunk_walk &w)
+{
+	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	int seg = -1;
+
+	if (!a.twin8)
+		return;
+	if (blockIdx.x == 0)
+		for (int s = threadIdx.x; s < a.n_seg; s += blockDim.x)
+			if (a.seg_flags[s] & ANNI_SEG_TWIN_FP8)
+				a.seg_scale[s] = fp8_scale(a.seg_amax[s]);
+	for (uint64_t it = 0; it < w.iters; it++) {
+		const uint64_t c = walk_chunk(w, it);
+		const uint64_t base = c * ANNI_CHUNK;
+		const int64_t abase = (int64_t)(a.arena_off + base);
+
+		if (c >= w.chunks)
+			continue;
+		if (seg < 0)
+			seg = seg_find(a.seg_off, a.n_seg, abase);
+		while (abase >= a.seg_off[seg + 1])
+			seg++;
+		if (a.aligned && base + ANNI_CHUNK <= a.n && abase + ANNI_CHUNK <= a.seg_off[seg + 1]) {
+			if (a.seg_flags[seg] & ANNI_SEG_TWIN_FP8) {
+				const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[seg]));
+				const uint64_t e = base + t8;
+				f32x8 p = io8<float>::load(a.master, e);
+				uint2 q;
+
+				q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[0] * inv, p.x[1] * inv),
+				    __NV_SATFINITE, __NV_E4M3)
+				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[2] * inv,
+				    p.x[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+				q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[4] * inv, p.x[5] * inv),
+				    __NV_SATFINITE, __NV_E4M3)
+				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[6] * inv,
+				    p.x[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+				__stcs(reinterpret_cast<uint2 *>(a.twin8 + e), q);
+			}
+		} else {
+			for (int k = 0; k < ANNI_VEC; k++) {
+				const uint64_t i = base + t8 + k;
+
+				if (i >= a.n)
+					break;
+				const int s = seg_find(a.seg_off, a.n_seg, (int64_t)(a.arena_off + i));
+
+				if (a.seg_flags[s] & ANNI_SEG_TWIN_FP8) {
+					const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[s]));
+
+					a.twin8[i] = (uint8_t)__nv_cvt_float_to_fp8(a.master[i] * inv,
+					    __NV_SATFINITE, __NV_E4M3);
+				}
+			}
+		}
+	}
+}
+
+/* ---- epilogue: the last block to finish closes the step --------------------- */
+
+__device__ __forceinline__ void step_epilogue(anni_control *ctl, bool skipped)
+{
+	__syncthreads();
+	if (threadIdx.x != 0)
+		return;
+	__threadfence();
+	if (atomicAdd(&ctl->done_ticket, 1u) != gridDim.x - 1)
+		return;
+	/* every block has read the loss scale and passed every barrier by now */
+	if (ctl->loss_scale > 0.0) {
+		if (skipped) {
+			double s = ctl->loss_scale * ctl->ls_backoff;
+
+			ctl->loss_scale = s < ctl->ls_min ? ctl->ls_min : s;
+			ctl->good_steps = 0;
+		} else if (++ctl->good_steps >= ctl->ls_interval && ctl->ls_interval > 0) {
+			double s = ctl->loss_scale * ctl->ls_growth;
+
+			ctl->loss_scale = s > ctl->ls_max ? ctl->ls_max : s;
+			ctl->good_steps = 0;
+		}
+	}
+	ctl->steps_done++;
+	ctl->bar_count = 0;
+	ctl->done_ticket = 0;
+	__threadfence();
+}
+
+/* ---- kernels ------------------------------------------------------------------ */
+
+/* Norm only (first launch of the split sequence): {sumsq, nonfinite} -> ctl->reduce. */
+template <typename GradT>
+__global__ void __launch_bounds__(ANNI_THREADS, 4) norm_kernel(const anni_launch a)
+{
+	__shared__ int s_last;
+	const chunk_walk w = walk_init(a.n, a.sc_log2);
+	double s;
+
+	s = block_sum(norm_phase<GradT>(a, w));
+	if (threadIdx.x == 0) {
+		a.ctl->partials[blockIdx.x] = s;
+		__threadfence();
+		s_last = atomicAdd(&a.ctl->norm_ticket, 1u) == gridDim.x - 1;
+	}
+	__syncthreads();
+	if (s_last) {
+		/* last block: every partial is visible; same fixed order as the fused kernel */
+		double t;
+
+		__threadfence();
+		t = sum_partials(a.ctl, (int)gridDim.x);
+		if (threadIdx.x == 0) {
+			a.ctl->reduce[0] = t;
+			a.ctl->reduce[1] = isfinite(t) ? 0.0 : 1.0;
+			a.ctl->norm_ticket = 0;
+		}
+	}
+}
+
+/* Update only (second launch of the split sequence, or the legacy call with a host multiplier). */
+template <typename GradT, typename StateT>
+__global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_launch a)
+{
+	const chunk_walk w = walk_init(a.n, a.sc_log2);
+	decision d;
+
+	if (a.flags & ANNI_LAUNCH_HOST_COEF) {
+		d.coef = a.grad_scale;
+		d.norm = 0.0;
+		d.skip = false;
+	} else {
+		d = decide(a, a.ctl->reduce[0], a.ctl->reduce[1], a.ctl->loss_scale);
+		if (blockIdx.x == 0 && threadIdx.x == 0) {
+			a.ctl->norm = d.norm;
+			a.ctl->eff_scale = d.coef;
+			a.ctl->skipped = d.skip ? 1 : 0;
+		}
+	}
+	update_phase<GradT, StateT>(a, w, d);
+	step_epilogue(a.ctl, d.skip);
+}
+
+/* The whole step in one cooperative launch. */
+template <typename GradT, typename StateT>
+__global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launch a)
+{
+	const chunk_walk w = walk_init(a.n, a.sc_log2);
+	decision d;
+	double ss = 0.0;
+	uint32_t barriers = 0;
+	const double loss_scale = a.ctl->loss_scale;
+
+	if (a.flags & ANNI_LAUNCH_NEED_NORM) {
+		double s = block_sum(norm_phase<GradT>(a, w));
+
+		if (threadIdx.x == 0)
+			a.ctl->partials[blockIdx.x] = s;
+		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
+			return;
+		ss = sum_partials(a.ctl, (int)gridDim.x);
+	}
+	d = decide(a, ss, 0.0, loss_scale);
+	if (blockIdx.x == 0 && threadIdx.x == 0) {
+		a.ctl->reduce[0] = ss;
+		a.ctl->reduce[1] = isfinite(ss) ? 0.0 : 1.0;
+		a.ctl->norm = d.norm;
+		a.ctl->eff_scale = d.coef;
+		a.ctl->skipped = d.skip ? 1 : 0;
+	}
+	update_phase<GradT, StateT>(a, w, d);
+	if ((a.flags & ANNI_LAUNCH_HAS_FP8) && !d.skip) {
+		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
+			return;
+		quantize_phase(a, w);
+	}
+	step_epilogue(a.ctl, d.skip);
+}
+
+/* e4m3 twins only (third launch of the split sequence). */
+__global__ void __launch_bounds__(ANNI_THREADS, 4) quantize_kernel(const anni_launch a)
+{
+	if (a.ctl->skipped)
+		return;
+	quantize_phase(a, walk_init(a.n, a.sc_log2));
+}
+
+/* One-shot fp32 -> bf16 of a flat buffer (seeding the twin; num/gpu.h:73 of the reference). */
+__global__ void __launch_bounds__(ANNI_THREADS) f32_to_bf16_kernel(uint16_t *dst, const float *src,
+	uint64_t n, int aligned)
+{
+	const uint64_t stride = (uint64_t)gridDim.x * ANNI_CHUNK;
+
+	for (uint64_t e = (uint64_t)blockIdx.x * ANNI_CHUNK + (uint64_t)threadIdx.x * ANNI_VEC; e < n;
+	    e += stride) {
+		if (aligned && e + ANNI_VEC <= n)
+			io8<__nv_bfloat16>::store(dst, e, io8<float>::load(src, e));
+		else
+			for (int k = 0; k < ANNI_VEC && e + k < n; k++)
+				io8<__nv_bfloat16>::store1(dst, e + k, src[e + k]);
+	}
+}
+
+/* y += a x (num/gpu.h:299 of the reference, gpu_mat_axpy). */
+__global__ void __launch_bounds__(ANNI_THREADS) axpy_kernel(float *y, const float *x, float a,
+	uint64_t n)
+{
+	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+		y[i] = fmaf(a, x[i], y[i]);
+}
+
+std::atomic<uint64_t> g_launches{0};
+
+template <typename K> int occupancy_blocks(K kernel)
+{
+	int dev = 0;
+	int sms = 0;
+	int per_sm = 0;
+
+	if (cudaGetDevice(&dev) != cudaSuccess
+	    || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess
+	    || cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ANNI_THREADS, 0)
+	    != cudaSuccess || sms <= 0 || per_sm <= 0)
+		return -1;
+	int blocks = sms * per_sm;
+
+	return blocks > ANNI_MAX_BLOCKS ? ANNI_MAX_BLOCKS / sms * sms : blocks;
+}
+
+template <typename GradT, typename StateT>
+int launch_update_t(const anni_launch *a, int blocks, cudaStream_t st)
+{
+	update_kernel<GradT, StateT><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+template <typename GradT, typename StateT>
+int launch_fused_t(const anni_launch *a, int blocks, cudaStream_t st)
+{
+	void *args[] = { (void *)a };
+
+	return cudaLaunchCooperativeKernel((const void *)fused_kernel<GradT, StateT>, dim3(blocks),
+	    dim3(ANNI_THREADS), args, 0, st) == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+}	/* namespace */
+
+extern "C" void anni_count_launch(void)
+{
+	g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+extern "C" uint64_t anni_kernel_launches(void)
+{
+	return g_launches.load(std::memory_order_relaxed);
+}
+
+extern "C" int anni_grid_blocks(int grad_dtype, int state_dtype, int cooperative)
+{
+	const bool gb = grad_dtype == ANNI_DT_BF16;
+	const bool sb = state_dtype == ANNI_DT_BF16;
+
+	if (cooperative) {
+		if (gb && sb)
+			return occupancy_blocks(fused_kernel<__nv_bfloat16, __nv_bfloat16>);
+		if (gb)
+			return occupancy_blocks(fused_kernel<__nv_bfloat16, float>);
+		if (sb)
+			return occupancy_blocks(fused_kernel<float, __nv_bfloat16>);
+		return occupancy_blocks(fused_kernel<float, float>);
+	}
+	if (gb && sb)
+		return occupancy_blocks(update_kernel<__nv_bfloat16, __nv_bfloat16>);
+	if (gb)
+		return occupancy_blocks(update_kernel<__nv_bfloat16, float>);
+	if (sb)
+		return occupancy_blocks(update_kernel<float, __nv_bfloat16>);
+	return occupancy_blocks(update_kernel<float, float>);
+}
+
+/*
+** Host side of the arithmetic contract: everything that depends only on the
+** step's scalars is computed once, in double, and rounded once.  Rejections
+** are those of the reference launcher (num/gpu_cuda.cu:8675-8682): lr <= 0,
+** t < 1, a bias correction that is not positive.
+*/
+extern "C" int anni_fill_hyper(anni_launch *a, const anni_optstep_hyper *hp)
+{
+	double bc1;
+	double bc2;
+
+	if (!a || !hp || !(hp->lr > 0.0) || hp->t < 1)
+		return ANNI_E_ARG;
+	bc1 = 1.0 - pow(hp->beta1, (double)hp->t);
+	bc2 = 1.0 - pow(hp->beta2, (double)hp->t);
+	if (!(bc1 > 0.0) || !(bc2 > 0.0))
+		return ANNI_E_ARG;
+	a->grad_scale = hp->grad_scale;
+	a->clip = hp->grad_clip > 0.0 ? hp->grad_clip : 0.0;
+	a->b1 = hp->beta1;
+	a->omb1 = 1.0 - hp->beta1;
+	a->b2 = hp->beta2;
+	a->omb2 = 1.0 - hp->beta2;
+	a->lrbc1 = (float)(hp->lr / bc1);
+	a->ibc2 = (float)(1.0 / bc2);
+	a->eps = (float)hp->eps;
+	a->lrwd = hp->weight_decay > 0.0 ? (float)(hp->lr * hp->weight_decay) : 0.0f;
+	a->flags = (a->flags & ~0xff) | (hp->flags & 0xff);
+	if (a->clip > 0.0 || (hp->flags & ANNI_STEP_CHECK_FINITE))
+		a->flags |= ANNI_LAUNCH_NEED_NORM;
+	else
+		a->flags &= ~ANNI_LAUNCH_NEED_NORM;
+	return ANNI_OK;
+}
+
+extern "C" int anni_launch_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st)
+{
+	if (!a || blocks < 1 || blocks > ANNI_MAX_BLOCKS)
+		return ANNI_E_ARG;
+	if (grad_dtype == ANNI_DT_BF16)
+		norm_kernel<__nv_bfloat16><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	else
+		norm_kernel<float><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+extern "C" int anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
+	cudaStream_t st)
+{
+	const bool gb = grad_dtype == ANNI_DT_BF16;
+	const bool sb = state_dtype == ANNI_DT_BF16;
+
+	if (!a || blocks < 1 || blocks > ANNI_MAX_BLOCKS)
+		return ANNI_E_ARG;
+	anni_count_launch();
+	if (gb && sb)
+		return launch_update_t<__nv_bfloat16, __nv_bfloat16>(a, blocks, st);
+	if (gb)
+		return launch_update_t<__nv_bfloat16, float>(a, blocks, st);
+	if (sb)
+		return launch_update_t<float, __nv_bfloat16>(a, blocks, st);
+	return launch_update_t<float, float>(a, blocks, st);
+}
+
+extern "C" int anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
+	cudaStream_t st)
+{
+	const bool gb = grad_dtype == ANNI_DT_BF16;
+	const bool sb = state_dtype == ANNI_DT_BF16;
+
+	if (!a || blocks < 1 || blocks > ANNI_MAX_BLOCKS)
+		return ANNI_E_ARG;
+	anni_count_launch();
+	if (gb && sb)
+		return launch_fused_t<__nv_bfloat16, __nv_bfloat16>(a, blocks, st);
+	if (gb)
+		return launch_fused_t<__nv_bfloat16, float>(a, blocks, st);
+	if (sb)
+		return launch_fused_t<float, __nv_bfloat16>(a, blocks, st);
+	return launch_fused_t<float, float>(a, blocks, st);
+}
+
+extern "C" int anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st)
+{
+	if (!a || blocks < 1 || blocks > ANNI_MAX_BLOCKS)
+		return ANNI_E_ARG;
+	quantize_kernel<<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+static int flat_blocks(uint64_t n)
+{
+	int dev = 0;
+	int sms = 148;
+	uint64_t want = (n + ANNI_CHUNK - 1) / ANNI_CHUNK;
+
+	if (cudaGetDevice(&dev) == cudaSuccess)
+		cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+	if (want > (uint64_t)sms * 8)
+		want = (uint64_t)sms * 8;
+	return want < 1 ? 1 : (int)want;
+}
+
+extern "C" int anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st)
+{
+	const int aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
+
+	if (!dst || !src || n == 0)
+		return ANNI_E_ARG;
+	f32_to_bf16_kernel<<<flat_blocks(n), ANNI_THREADS, 0, st>>>(dst, src, n, aligned);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+extern "C" int anni_launch_axpy(float *y, const float *x, float a, uint64_t n, cudaStream_t st)
+{
+	if (!y || !x || n == 0)
+		return ANNI_E_ARG;
+	axpy_kernel<<<flat_blocks(n), ANNI_THREADS, 0, st>>>(y, x, a, n);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}

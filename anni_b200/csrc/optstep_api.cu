@@ -1,0 +1,312 @@
+/*
+** Host side of the packed-arena engine: life cycle, argument checks and the
+** launch sequences behind the anni_optstep_* entry points of anni_b200.h.
+** No arithmetic on parameters happens on the host; a missing device is an
+** error, never a reason to compute on the CPU.
+*/
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdlib.h>
+#include <string.h>
+#include "optstep_internal.h"
+
+struct anni_optstep {
+	anni_optstep_config	cfg;
+	anni_launch		la;		/* buffers + tables, hyper filled per step */
+	anni_control		*ctl;		/* device */
+	int64_t			*d_seg_off;
+	uint32_t		*d_seg_flags;
+	float			*d_amax;
+	float			*d_scale;
+	int			n_seg;
+	int			has_fp8;
+	int			bound;
+	int			device;
+	int			blocks_coop;
+	int			blocks_split;
+};
+
+/* ANNI_B200_SUPERCHUNK=k: 2^k consecutive chunks per block per round (tuning knob). */
+static int superchunk_log2(void)
+{
+	const char *e = getenv("ANNI_B200_SUPERCHUNK");
+	int k = e ? atoi(e) : 2;
+
+	return k < 0 ? 0 : (k > 20 ? 20 : k);
+}
+
+static int check_cfg(const anni_optstep_config *c)
+{
+	int i;
+
+	if (!c || c->shard_off > c->n_arena || c->shard_n > c->n_arena - c->shard_off)
+		return ANNI_E_ARG;
+	if ((c->grad_dtype != ANNI_DT_F32 && c->grad_dtype != ANNI_DT_BF16)
+	    || (c->state_dtype != ANNI_DT_F32 && c->state_dtype != ANNI_DT_BF16))
+		return ANNI_E_ARG;
+	if (c->n_seg < 0 || (c->n_seg > 0 && (!c->seg_off || !c->seg_flags)))
+		return ANNI_E_ARG;
+	if (c->n_seg > 0) {
+		if (c->seg_off[0] != 0 || (uint64_t)c->seg_off[c->n_seg] != c->n_arena)
+			return ANNI_E_ARG;
+		for (i = 0; i < c->n_seg; i++)
+			if (c->seg_off[i + 1] < c->seg_off[i])
+				return ANNI_E_ARG;
+	}
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep **out)
+{
+	anni_optstep *h;
+	int64_t one_off[2];
+	uint32_t one_flag = ANNI_SEG_WD | ANNI_SEG_TWIN_BF16;
+	const int64_t *off;
+	const uint32_t *flg;
+	int rc;
+	int i;
+
+	if (!out)
+		return ANNI_E_ARG;
+	*out = NULL;
+	rc = check_cfg(cfg);
+	if (rc != ANNI_OK)
+		return rc;
+	h = (anni_optstep *)calloc(1, sizeof(*h));
+	if (!h)
+		return ANNI_E_NOMEM;
+	h->cfg = *cfg;
+	h->cfg.seg_off = NULL;
+	h->cfg.seg_flags = NULL;
+	if (cudaGetDevice(&h->device) != cudaSuccess) {
+		free(h);
+		return ANNI_E_CUDA;
+	}
+	if (cfg->n_seg > 0) {
+		h->n_seg = cfg->n_seg;
+		off = cfg->seg_off;
+		flg = cfg->seg_flags;
+	} else {
+		h->n_seg = 1;
+		one_off[0] = 0;
+		one_off[1] = (int64_t)cfg->n_arena;
+		off = one_off;
+		flg = &one_flag;
+	}
+	for (i = 0; i < h->n_seg; i++)
+		if (flg[i] & ANNI_SEG_TWIN_FP8)
+			h->has_fp8 = 1;
+	if (cudaMalloc((void **)&h->ctl, sizeof(anni_control)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_seg_off, (size_t)(h->n_seg + 1) * sizeof(int64_t)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_seg_flags, (size_t)h->n_seg * sizeof(uint32_t)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_amax, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_scale, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
+	    || cudaMemset(h->ctl, 0, sizeof(anni_control)) != cudaSuccess
+	    || cudaMemset(h->d_amax, 0, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
+	    || cudaMemset(h->d_scale, 0, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
+	    || cudaMemcpy(h->d_seg_off, off, (size_t)(h->n_seg + 1) * sizeof(int64_t),
+	    cudaMemcpyHostToDevice) != cudaSuccess
+	    || cudaMemcpy(h->d_seg_flags, flg, (size_t)h->n_seg * sizeof(uint32_t),
+	    cudaMemcpyHostToDevice) != cudaSuccess) {
+		anni_optstep_destroy(h);
+		return ANNI_E_CUDA;
+	}
+	h->blocks_coop = anni_grid_blocks(cfg->grad_dtype, cfg->state_dtype, 1);
+	h->blocks_split = anni_grid_blocks(cfg->grad_dtype, cfg->state_dtype, 0);
+	if (h->blocks_coop < 1 || h->blocks_split < 1) {
+		anni_optstep_destroy(h);
+		return ANNI_E_CUDA;
+	}
+	/* same geometry for both forms: identical block partials, identical norm bits */
+	if (h->blocks_split > h->blocks_coop)
+		h->blocks_split = h->blocks_coop;
+	else
+		h->blocks_coop = h->blocks_split;
+	h->la.n = cfg->shard_n;
+	h->la.arena_off = cfg->shard_off;
+	h->la.seg_off = h->d_seg_off;
+	h->la.seg_flags = h->d_seg_flags;
+	h->la.seg_amax = h->d_amax;
+	h->la.seg_scale = h->d_scale;
+	h->la.n_seg = h->n_seg;
+	h->la.ctl = h->ctl;
+	h->la.sc_log2 = superchunk_log2();
+	*out = h;
+	return ANNI_OK;
+}
+
+extern "C" void anni_optstep_destroy(anni_optstep *h)
+{
+	if (!h)
+		return;
+	cudaFree(h->ctl);
+	cudaFree(h->d_seg_off);
+	cudaFree(h->d_seg_flags);
+	cudaFree(h->d_amax);
+	cudaFree(h->d_scale);
+	free(h);
+}
+
+extern "C" int anni_optstep_bind(anni_optstep *h, const anni_optstep_buffers *b)
+{
+	uintptr_t bits;
+
+	if (!h || !b)
+		return ANNI_E_ARG;
+	if (h->cfg.shard_n > 0 && (!b->master || !b->m || !b->v || !b->grad))
+		return ANNI_E_ARG;
+	if (h->has_fp8 && h->cfg.shard_n > 0 && !b->twin_fp8)
+		return ANNI_E_ARG;
+	bits = (uintptr_t)b->master | (uintptr_t)b->m | (uintptr_t)b->v | (uintptr_t)b->grad
+	    | (uintptr_t)b->twin_bf16 | (uintptr_t)b->twin_fp8;
+	h->la.master = b->master;
+	h->la.m = b->m;
+	h->la.v = b->v;
+	h->la.grad = b->grad;
+	h->la.twin16 = (uint16_t *)b->twin_bf16;
+	h->la.twin8 = (uint8_t *)b->twin_fp8;
+	h->la.aligned = (bits & 15) == 0;
+	h->bound = 1;
+	return ANNI_OK;
+}
+
+static int prepare(anni_optstep *h, const anni_optstep_hyper *hp, anni_launch *la)
+{
+	int rc;
+
+	if (!h || !hp || !h->bound)
+		return ANNI_E_ARG;
+	*la = h->la;
+	la->flags = h->has_fp8 ? ANNI_LAUNCH_HAS_FP8 : 0;
+	rc = anni_fill_hyper(la, hp);
+	return rc;
+}
+
+extern "C" int anni_optstep_step(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
+{
+	anni_launch la;
+	cudaStream_t st = (cudaStream_t)stream;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
+	    != cudaSuccess)
+		return ANNI_E_CUDA;
+	return anni_launch_fused(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_coop, st);
+}
+
+extern "C" int anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
+{
+	anni_launch la;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	return anni_launch_norm(&la, h->cfg.grad_dtype, h->blocks_split, (cudaStream_t)stream);
+}
+
+extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
+{
+	anni_launch la;
+	cudaStream_t st = (cudaStream_t)stream;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
+	    != cudaSuccess)
+		return ANNI_E_CUDA;
+	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+}
+
+extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
+{
+	anni_launch la;
+
+	if (!h || !h->bound)
+		return ANNI_E_ARG;
+	if (!h->has_fp8)
+		return ANNI_OK;
+	la = h->la;
+	la.flags = ANNI_LAUNCH_HAS_FP8;
+	return anni_launch_quantize(&la, h->blocks_split, (cudaStream_t)stream);
+}
+
+extern "C" double *anni_optstep_reduce_buffer(anni_optstep *h)
+{
+	return h ? (double *)((char *)h->ctl + offsetof(anni_control, reduce)) : NULL;
+}
+
+extern "C" float *anni_optstep_amax_buffer(anni_optstep *h)
+{
+	return h ? h->d_amax : NULL;
+}
+
+extern "C" float *anni_optstep_scale_buffer(anni_optstep *h)
+{
+	return h ? h->d_scale : NULL;
+}
+
+extern "C" int anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *stream)
+{
+	anni_control head;	/* only the scalars in front of partials[] are copied */
+	const size_t nb = offsetof(anni_control, partials);
+
+	if (!h || !out)
+		return ANNI_E_ARG;
+	if (cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess
+	    || cudaMemcpy(&head, h->ctl, nb, cudaMemcpyDeviceToHost) != cudaSuccess)
+		return ANNI_E_CUDA;
+	out->sumsq = head.reduce[0];
+	out->norm = head.norm;
+	out->eff_scale = head.eff_scale;
+	out->loss_scale = head.loss_scale;
+	out->skipped = head.skipped;
+	out->error = head.error;
+	out->good_steps = head.good_steps;
+	out->steps_done = head.steps_done;
+	if (head.error != 0) {
+		/* a bounded wait gave up: clear the counters so the engine can be used again */
+		head.error = 0;
+		head.bar_count = 0;
+		head.norm_ticket = 0;
+		head.done_ticket = 0;
+		if (cudaMemcpy(h->ctl, &head, nb, cudaMemcpyHostToDevice) != cudaSuccess)
+			return ANNI_E_CUDA;
+	}
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_loss_scale_init(anni_optstep *h, double scale, int growth_interval,
+	double growth, double backoff, double min_scale, double max_scale)
+{
+	anni_control head;
+	const size_t nb = offsetof(anni_control, partials);
+
+	if (!h)
+		return ANNI_E_ARG;
+	if (cudaDeviceSynchronize() != cudaSuccess
+	    || cudaMemcpy(&head, h->ctl, nb, cudaMemcpyDeviceToHost) != cudaSuccess)
+		return ANNI_E_CUDA;
+	head.loss_scale = scale > 0.0 ? scale : 0.0;
+	head.ls_interval = growth_interval;
+	head.ls_growth = growth;
+	head.ls_backoff = backoff;
+	head.ls_min = min_scale;
+	head.ls_max = max_scale;
+	head.good_steps = 0;
+	return cudaMemcpy(h->ctl, &head, nb, cudaMemcpyHostToDevice) == cudaSuccess
+	    ? ANNI_OK : ANNI_E_CUDA;
+}
+
+extern "C" int anni_optstep_grid(anni_optstep *h, int *blocks, int *threads)
+{
+	if (!h)
+		return ANNI_E_ARG;
+	if (blocks)
+		*blocks = h->blocks_coop;
+	if (threads)
+		*threads = ANNI_THREADS;
+	return ANNI_OK;
+}

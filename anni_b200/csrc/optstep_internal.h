@@ -1,0 +1,102 @@
+/*
+** Internal interface between the packed-arena engine (optstep.cu) and the
+** reference-compatible device API (gpu_compat.cu).  Not installed.
+*/
+#ifndef ANNI_OPTSTEP_INTERNAL_H__
+#define ANNI_OPTSTEP_INTERNAL_H__
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "anni_b200.h"
+
+#define ANNI_THREADS		256	/* threads per block of every arena kernel */
+#define ANNI_VEC		8	/* elements per thread per chunk */
+#define ANNI_CHUNK		(ANNI_THREADS * ANNI_VEC)
+#define ANNI_MAX_BLOCKS		2048	/* capacity of the per-block partial table */
+/* polls of a bounded device wait before it gives up (each poll sleeps >= 32 ns) */
+#define ANNI_WAIT_POLLS		(1u << 23)
+
+/*
+** Device-resident control block of one engine (or of the legacy entry points).
+** Everything the kernels exchange besides the big buffers lives here.
+*/
+typedef struct anni_control {
+	double		reduce[2];	/* {sum of squares, non-finite count}; all-reduced by ZeRO-1 callers */
+	double		norm;
+	double		eff_scale;
+	double		loss_scale;	/* <= 0: state machine off */
+	double		ls_growth;
+	double		ls_backoff;
+	double		ls_min;
+	double		ls_max;
+	int32_t		ls_interval;
+	int32_t		good_steps;
+	int32_t		skipped;
+	int32_t		error;
+	int32_t		steps_done;
+	uint32_t	bar_count;	/* arrivals at the in-kernel barriers; reset by the last block */
+	uint32_t	norm_ticket;	/* blocks that finished the norm kernel */
+	uint32_t	done_ticket;	/* blocks that finished the update */
+	double		partials[ANNI_MAX_BLOCKS];
+} anni_control;
+
+/* Arguments of one launch, passed by value. */
+typedef struct anni_launch {
+	float		*master;
+	void		*m;
+	void		*v;
+	void		*grad;
+	uint16_t	*twin16;
+	uint8_t		*twin8;
+	uint64_t	n;		/* shard elements */
+	uint64_t	arena_off;	/* arena coordinate of shard element 0 */
+	const int64_t	*seg_off;	/* device, n_seg + 1 */
+	const uint32_t	*seg_flags;	/* device, n_seg */
+	float		*seg_amax;	/* device, n_seg */
+	float		*seg_scale;	/* device, n_seg */
+	int		n_seg;
+	int		flags;		/* ANNI_STEP_* | ANNI_LAUNCH_* */
+	int		aligned;	/* every buffer 16-byte aligned: vector path allowed */
+	int		sc_log2;	/* log2 of the chunks per super-chunk (see walk_chunk) */
+	double		grad_scale;
+	double		clip;
+	double		b1;
+	double		omb1;
+	double		b2;
+	double		omb2;
+	float		lrbc1;		/* lr / (1 - beta1^t) */
+	float		ibc2;		/* 1 / (1 - beta2^t) */
+	float		eps;
+	float		lrwd;		/* lr * weight_decay */
+	anni_control	*ctl;
+} anni_launch;
+
+/* launch flags beyond ANNI_STEP_* */
+#define ANNI_LAUNCH_HOST_COEF	0x100	/* grad_scale is final: no norm, no decision (legacy two-call sequence) */
+#define ANNI_LAUNCH_NEED_NORM	0x200	/* the norm feeds a clip or a finite check */
+#define ANNI_LAUNCH_HAS_FP8	0x400	/* some segment asks for an e4m3 twin */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernel launchers (optstep.cu).  `blocks` must not exceed ANNI_MAX_BLOCKS. */
+int	anni_launch_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
+int	anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
+		cudaStream_t st);
+int	anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
+		cudaStream_t st);
+int	anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st);
+int	anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st);
+int	anni_launch_axpy(float *y, const float *x, float a, uint64_t n, cudaStream_t st);
+/* Persistent-grid size for the given kernel family on the current device. */
+int	anni_grid_blocks(int grad_dtype, int state_dtype, int cooperative);
+/* Fills the hyper-parameter part of a launch; ANNI_E_ARG on values the reference rejects. */
+int	anni_fill_hyper(anni_launch *a, const anni_optstep_hyper *hp);
+void	anni_count_launch(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

@@ -1,0 +1,292 @@
+"""Host-side mirror of the reference optimizer's interface over the packed arena.
+
+Names follow the reference (``lang/lm_adam.h``): an optimizer owns flat device
+buffers ``d_param / d_grad / d_m / d_v / d_param_bf16`` indexed by one running element
+offset per tensor ("segment"), in the order ``lm_adam_create`` walks the model
+(``lang/lm_adam.c:117-136``).  Here torch only provides device memory and streams; all
+arithmetic happens inside ``libanni_b200.so``.
+"""
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import capi
+from .capi import (DT_BF16, DT_F32, SEG_TWIN_BF16, SEG_TWIN_FP8, SEG_WD, STEP_CHECK_FINITE,
+                   STEP_DEV_LOSS_SCALE, STEP_ZERO_GRAD, check)
+
+
+# ---------------------------------------------------------------------------------
+# segment tables
+# ---------------------------------------------------------------------------------
+
+@dataclass
+class Segments:
+    """Packed-arena layout: per tensor a name, an element count and ANNI_SEG_* flags."""
+    names: List[str] = field(default_factory=list)
+    sizes: List[int] = field(default_factory=list)
+    flags: List[int] = field(default_factory=list)
+
+    def add(self, name, n, flags):
+        self.names.append(name)
+        self.sizes.append(int(n))
+        self.flags.append(int(flags))
+
+    @property
+    def n(self):
+        return int(sum(self.sizes))
+
+    @property
+    def offsets(self):
+        return np.concatenate([[0], np.cumsum(np.asarray(self.sizes, dtype=np.int64))]).astype(np.int64)
+
+    @property
+    def flag_array(self):
+        return np.asarray(self.flags, dtype=np.uint32)
+
+    def __len__(self):
+        return len(self.sizes)
+
+    def index(self, name):
+        return self.names.index(name)
+
+    def slice_of(self, name):
+        i = self.index(name)
+        off = self.offsets
+        return slice(int(off[i]), int(off[i + 1]))
+
+
+def lm_segments(d_model, d_ff, n_blocks, vocab, tied, *, wd="matrices", twin="bf16",
+                attn_bias=False):
+    """Segment list of a decoder-only LM in the reference's optimizer order.
+
+    Order and shapes: ``lang/lm_adam.c:117-136`` -- ``w_head`` (D x V), ``b_head`` (V),
+    the embedding table (V x D) when untied, then per block ``wq wk wv wo`` (D x D),
+    ``w1`` (D x FF), ``b1``, ``w2`` (FF x D), ``b2``, ``ln1.gamma ln1.beta ln2.gamma
+    ln2.beta``.  ``wd`` selects where decoupled decay applies: "matrices" (the benchmark
+    configuration's wording) or "all" (what the reference kernels do,
+    ``num/gpu_cuda.cu:8553``).  ``twin``: "bf16" for every tensor, or "fp8" = e4m3 for the
+    block matrices with bf16 kept for vectors, the head and the embedding.
+    ``attn_bias`` adds the four per-block attention bias vectors the benchmark wording
+    mentions and the reference model does not have.
+    """
+    s = Segments()
+    D, FF, V = d_model, d_ff, vocab
+
+    def mat(name, n, fp8_ok=True):
+        f = SEG_WD if wd in ("matrices", "all") else 0
+        if twin == "fp8" and fp8_ok:
+            f |= SEG_TWIN_FP8
+        elif twin in ("bf16", "fp8"):
+            f |= SEG_TWIN_BF16
+        s.add(name, n, f)
+
+    def vec(name, n):
+        f = SEG_WD if wd == "all" else 0
+        if twin in ("bf16", "fp8"):
+            f |= SEG_TWIN_BF16
+        s.add(name, n, f)
+
+    mat("w_head", D * V, fp8_ok=False)
+    vec("b_head", V)
+    if not tied:
+        mat("embed", V * D, fp8_ok=False)
+    for b in range(n_blocks):
+        for w in ("wq", "wk", "wv", "wo"):
+            mat(f"blk{b}.{w}", D * D)
+            if attn_bias:
+                vec(f"blk{b}.b{w[1]}", D)
+        mat(f"blk{b}.w1", D * FF)
+        vec(f"blk{b}.b1", FF)
+        mat(f"blk{b}.w2", FF * D)
+        vec(f"blk{b}.b2", D)
+        for v_ in ("ln1.gamma", "ln1.beta", "ln2.gamma", "ln2.beta"):
+            vec(f"blk{b}.{v_}", D)
+    return s
+
+
+# the benchmark configurations' shapes (element counts follow lm_param_count, lang/lm_adam.c:59-77)
+LM_SHAPES = {
+    "talk170m": dict(d_model=1024, d_ff=4096, n_blocks=12, vocab=16384, tied=False),   # 184,676,352
+    "run555m": dict(d_model=1536, d_ff=6272, n_blocks=14, vocab=100000, tied=True),    # 555,762,080
+    "synth3b": dict(d_model=2560, d_ff=10240, n_blocks=32, vocab=100000, tied=True),   # 2,773,419,680
+    "tiny": dict(d_model=64, d_ff=256, n_blocks=2, vocab=300, tied=False),             # 138,156 (the reference's unit-test LM)
+}
+
+
+def lm_param_count(d_model, d_ff, n_blocks, vocab, tied):
+    n = d_model * vocab + vocab
+    if not tied:
+        n += vocab * d_model
+    n += n_blocks * (4 * d_model * d_model + 2 * d_model * d_ff + d_ff + d_model + 4 * d_model)
+    return n
+
+
+# ---------------------------------------------------------------------------------
+# the engine
+# ---------------------------------------------------------------------------------
+
+_TORCH_DT = {DT_F32: torch.float32, DT_BF16: torch.bfloat16}
+
+
+class OptStep:
+    """One shard of the packed arena and the kernels that step it.
+
+    ``shard_off`` / ``shard_n`` select the arena elements this engine owns (the whole
+    arena by default).  Buffers are torch tensors on ``device``; pass your own with
+    ``bind`` or let ``allocate`` create zeroed ones.
+    """
+
+    def __init__(self, segments: Optional[Segments], *, n_arena=None, grad_dtype=DT_BF16,
+                 state_dtype=DT_F32, shard_off=0, shard_n=None, device="cuda"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("anni_b200 needs a CUDA device: there is no CPU path")
+        self.L = capi.lib()
+        self.device = torch.device(device)
+        self.segments = segments
+        self.n_arena = int(segments.n if segments is not None else n_arena)
+        self.shard_off = int(shard_off)
+        self.shard_n = int(self.n_arena - self.shard_off if shard_n is None else shard_n)
+        self.grad_dtype, self.state_dtype = grad_dtype, state_dtype
+        cfg = capi.Config()
+        cfg.n_arena, cfg.shard_off, cfg.shard_n = self.n_arena, self.shard_off, self.shard_n
+        cfg.grad_dtype, cfg.state_dtype = grad_dtype, state_dtype
+        if segments is not None and len(segments) > 0:
+            self._off = np.ascontiguousarray(segments.offsets)
+            self._flg = np.ascontiguousarray(segments.flag_array)
+            cfg.n_seg = len(segments)
+            cfg.seg_off = self._off.ctypes.data
+            cfg.seg_flags = self._flg.ctypes.data
+            self.n_seg = len(segments)
+            self.has_fp8 = bool((self._flg & SEG_TWIN_FP8).any())
+        else:
+            cfg.n_seg = 0
+            self.n_seg = 1
+            self.has_fp8 = False
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check("anni_optstep_create", self.L.anni_optstep_create(C.byref(cfg), C.byref(h)))
+        self.h = h
+        self.master = self.m = self.v = self.grad = self.twin_bf16 = self.twin_fp8 = None
+
+    # -- memory -----------------------------------------------------------------------
+    def allocate(self, twin_bf16=True, pad_to=None):
+        n = max(self.shard_n, 1) if pad_to is None else int(pad_to)
+        dev = self.device
+        master = torch.zeros(n, dtype=torch.float32, device=dev)
+        m = torch.zeros(n, dtype=_TORCH_DT[self.state_dtype], device=dev)
+        v = torch.zeros(n, dtype=_TORCH_DT[self.state_dtype], device=dev)
+        grad = torch.zeros(n, dtype=_TORCH_DT[self.grad_dtype], device=dev)
+        t16 = torch.zeros(n, dtype=torch.bfloat16, device=dev) if twin_bf16 else None
+        t8 = torch.zeros(n, dtype=torch.uint8, device=dev) if self.has_fp8 else None
+        self.bind(master, m, v, grad, t16, t8)
+        return self
+
+    def bind(self, master, m, v, grad, twin_bf16=None, twin_fp8=None):
+        for t in (master, m, v, grad, twin_bf16, twin_fp8):
+            if t is not None:
+                assert t.is_cuda and t.is_contiguous() and t.numel() >= self.shard_n
+        assert master.dtype == torch.float32
+        assert m.dtype == v.dtype == _TORCH_DT[self.state_dtype]
+        assert grad.dtype == _TORCH_DT[self.grad_dtype]
+        b = capi.Buffers()
+        b.master, b.m, b.v, b.grad = master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr()
+        b.twin_bf16 = twin_bf16.data_ptr() if twin_bf16 is not None else None
+        b.twin_fp8 = twin_fp8.data_ptr() if twin_fp8 is not None else None
+        check("anni_optstep_bind", self.L.anni_optstep_bind(self.h, C.byref(b)))
+        self.master, self.m, self.v, self.grad = master, m, v, grad
+        self.twin_bf16, self.twin_fp8 = twin_bf16, twin_fp8
+        return self
+
+    # -- stepping ---------------------------------------------------------------------
+    @staticmethod
+    def hyper(*, lr, t, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, clip=0.0, grad_scale=1.0,
+              check_finite=True, zero_grad=True, dev_loss_scale=False):
+        hp = capi.Hyper()
+        hp.lr, hp.beta1, hp.beta2, hp.eps = lr, beta1, beta2, eps
+        hp.weight_decay, hp.grad_clip, hp.grad_scale, hp.t = wd, clip, grad_scale, int(t)
+        hp.flags = ((STEP_CHECK_FINITE if check_finite else 0) | (STEP_ZERO_GRAD if zero_grad else 0)
+                    | (STEP_DEV_LOSS_SCALE if dev_loss_scale else 0))
+        return hp
+
+    def _stream(self, stream):
+        s = torch.cuda.current_stream(self.device) if stream is None else stream
+        return C.c_void_p(s.cuda_stream)
+
+    def step(self, hp, stream=None):
+        """The whole step in one cooperative launch (single-GPU form)."""
+        check("anni_optstep_step", self.L.anni_optstep_step(self.h, C.byref(hp), self._stream(stream)))
+
+    def norm(self, hp, stream=None):
+        check("anni_optstep_norm", self.L.anni_optstep_norm(self.h, C.byref(hp), self._stream(stream)))
+
+    def update(self, hp, stream=None):
+        check("anni_optstep_update", self.L.anni_optstep_update(self.h, C.byref(hp), self._stream(stream)))
+
+    def quantize(self, stream=None):
+        check("anni_optstep_quantize", self.L.anni_optstep_quantize(self.h, self._stream(stream)))
+
+    def step_split(self, hp, stream=None):
+        """Same result through the three-launch form (what ZeRO-1 interleaves with collectives)."""
+        self.norm(hp, stream)
+        self.update(hp, stream)
+        if self.has_fp8:
+            self.quantize(stream)
+
+    # -- small device buffers as tensors (for collectives) -----------------------------------
+    def _as_tensor(self, ptr, n, dtype):
+        """A torch view of library-owned device memory (no copy, not owned by torch)."""
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+
+        class _Holder:
+            pass
+        hold = _Holder()
+        hold.__cuda_array_interface__ = {
+            "shape": (n,), "typestr": {torch.float64: "<f8", torch.float32: "<f4"}[dtype],
+            "data": (int(ptr), False), "version": 3, "strides": None}
+        del nbytes
+        return torch.as_tensor(hold, device=self.device)
+
+    def reduce_tensor(self):
+        return self._as_tensor(self.L.anni_optstep_reduce_buffer(self.h), 2, torch.float64)
+
+    def amax_tensor(self):
+        return self._as_tensor(self.L.anni_optstep_amax_buffer(self.h), self.n_seg, torch.float32)
+
+    def scale_tensor(self):
+        return self._as_tensor(self.L.anni_optstep_scale_buffer(self.h), self.n_seg, torch.float32)
+
+    # -- status -------------------------------------------------------------------------
+    def status(self, stream=None):
+        st = capi.Status()
+        check("anni_optstep_status_read",
+              self.L.anni_optstep_status_read(self.h, C.byref(st), self._stream(stream)))
+        return st
+
+    def loss_scale_init(self, scale=65536.0, growth_interval=200, growth=2.0, backoff=0.5,
+                        min_scale=1.0, max_scale=2.0 ** 24):
+        check("anni_optstep_loss_scale_init",
+              self.L.anni_optstep_loss_scale_init(self.h, scale, growth_interval, growth, backoff,
+                                                  min_scale, max_scale))
+
+    def grid(self):
+        b, t = C.c_int(), C.c_int()
+        check("anni_optstep_grid", self.L.anni_optstep_grid(self.h, C.byref(b), C.byref(t)))
+        return b.value, t.value
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.L.anni_optstep_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def kernel_launches():
+    return int(capi.lib().anni_kernel_launches())

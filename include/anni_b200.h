@@ -1,0 +1,183 @@
+/*
+** anni_b200 -- B200 (sm_100a) optimizer-step engine for AnnI's decoder-only LM
+** trainer.  C ABI: plain pointers and sizes, no C++ or framework types.
+**
+** Two groups of entry points live in libanni_b200.so:
+**
+**  1. anni_optstep_*  (this header): the packed-arena engine.  One engine owns
+**     one contiguous shard of the flat parameter arena (the whole arena on one
+**     GPU, 1/N of it under ZeRO-1) and runs the step as a fused pass: global
+**     gradient-norm reduction, unscale + non-finite skip decision, AdamW with
+**     decoupled weight decay, fp32 master write, fp32 or bf16 moments, bf16 /
+**     fp8-e4m3 weight twins with per-tensor amax.  Every decision is taken on
+**     the device; the host never waits inside a step.
+**
+**  2. the reference's own device API (num/gpu.h of the reference project),
+**     declared in anni_gpu_compat.h: the ~20 symbols its optimizer calls get
+**     real bodies on top of the same kernels, the rest answer -1 / NULL like
+**     the reference's stub backend, so its trainer links unchanged.
+**
+** Error convention (that of num/gpu.h:78-80,134-139): int functions return 0
+** when the work was queued on the device and a negative value when nothing was
+** done.  There is no CPU fallback inside this library.
+*/
+#ifndef ANNI_B200_H__
+#define ANNI_B200_H__
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of the gradient and moment buffers */
+#define ANNI_DT_F32	0
+#define ANNI_DT_BF16	1
+
+/* per-segment flags */
+#define ANNI_SEG_WD		1u	/* decoupled weight decay applies to this tensor */
+#define ANNI_SEG_TWIN_BF16	2u	/* emit a bf16 twin (round to nearest even) */
+#define ANNI_SEG_TWIN_FP8	4u	/* emit an e4m3 twin with a per-tensor scale */
+
+/* per-step flags */
+#define ANNI_STEP_CHECK_FINITE	1	/* skip the step when the norm is not finite */
+#define ANNI_STEP_ZERO_GRAD	2	/* leave the gradient shard zeroed, as the reference step does */
+#define ANNI_STEP_DEV_LOSS_SCALE 4	/* divide grad_scale by the device-resident loss scale */
+
+/* error codes (negative return values; also anni_optstep_status.error) */
+#define ANNI_OK			0
+#define ANNI_E_ARG		(-1)	/* bad argument: nothing was launched */
+#define ANNI_E_CUDA		(-2)	/* a CUDA runtime call failed */
+#define ANNI_E_BARRIER_TIMEOUT	(-3)	/* a bounded device-side wait gave up; state untouched by late blocks */
+#define ANNI_E_NOMEM		(-4)
+#define ANNI_E_LIMIT		(-5)	/* size beyond a stated maximum */
+
+typedef struct anni_optstep anni_optstep;
+
+/*
+** Shape of one engine.  The arena is the reference's flat layout
+** (lang/lm_adam.c:217-311: one running element offset per tensor, unpadded, the
+** bf16 twin at the same element offset as the fp32 master, num/gpu_cuda.cu:
+** 2026-2034).  seg_off has n_seg + 1 ascending ARENA element offsets
+** (seg_off[0] = 0, seg_off[n_seg] = n_arena); both arrays are host memory and
+** are copied.  n_seg = 0 means one segment covering everything with
+** ANNI_SEG_WD | ANNI_SEG_TWIN_BF16, which is what the reference's flat kernels
+** do (num/gpu_cuda.cu:8557-8580).
+*/
+typedef struct anni_optstep_config {
+	uint64_t	n_arena;	/* elements in the whole arena */
+	uint64_t	shard_off;	/* first arena element this engine owns */
+	uint64_t	shard_n;	/* elements this engine owns (may be 0) */
+	int		grad_dtype;	/* ANNI_DT_* */
+	int		state_dtype;	/* ANNI_DT_*: storage of m and v */
+	int		n_seg;
+	const int64_t	*seg_off;
+	const uint32_t	*seg_flags;
+} anni_optstep_config;
+
+/*
+** Device buffers of the shard, caller-owned, each 16-byte aligned; element i of
+** every buffer is arena element shard_off + i.  twin_bf16 / twin_fp8 may be
+** NULL when no segment asks for that twin.
+*/
+typedef struct anni_optstep_buffers {
+	float	*master;	/* fp32 [shard_n], updated in place */
+	void	*m;		/* state_dtype [shard_n] */
+	void	*v;
+	void	*grad;		/* grad_dtype [shard_n] */
+	void	*twin_bf16;	/* uint16 [shard_n] */
+	void	*twin_fp8;	/* uint8  [shard_n] */
+} anni_optstep_buffers;
+
+/*
+** One step's scalars, named as in the reference (lang/lm_adam.h:37-53 and
+** the argument list at num/gpu.h:129-132).  t is the step number AFTER the
+** caller incremented it (t >= 1), exactly the `t` of gpu_adam_step_dev_bf16.
+** grad_scale multiplies every gradient (1/batch, and 1/loss_scale unless the
+** device-resident scale is used).  grad_clip = 0 turns clipping off.
+*/
+typedef struct anni_optstep_hyper {
+	double	lr;
+	double	beta1;
+	double	beta2;
+	double	eps;
+	double	weight_decay;
+	double	grad_clip;
+	double	grad_scale;
+	int	t;
+	int	flags;		/* ANNI_STEP_* */
+} anni_optstep_hyper;
+
+/* What the device decided, read back on request. */
+typedef struct anni_optstep_status {
+	double	sumsq;		/* sum of squares of the raw gradients (all ranks once reduced) */
+	double	norm;		/* sqrt(sumsq) * |effective grad scale|: the pre-clip norm (lm_adam.h:53) */
+	double	eff_scale;	/* multiplier actually applied to the gradients */
+	double	loss_scale;	/* device-resident loss scale after this step */
+	int32_t	skipped;	/* 1: non-finite norm, parameters and moments untouched */
+	int32_t	error;		/* ANNI_E_* raised on the device, 0 if none */
+	int32_t	good_steps;	/* clean steps since the loss scale last changed */
+	int32_t	steps_done;	/* update launches completed since creation */
+} anni_optstep_status;
+
+/* ---- life cycle ---------------------------------------------------------- */
+
+/* Creates an engine on the current CUDA device (allocates its small control
+** block and device copies of the segment table). */
+int	anni_optstep_create(const anni_optstep_config *cfg, anni_optstep **out);
+void	anni_optstep_destroy(anni_optstep *h);
+int	anni_optstep_bind(anni_optstep *h, const anni_optstep_buffers *buf);
+
+/* ---- the step -------------------------------------------------------------- */
+
+/*
+** Whole step in ONE cooperative launch on `stream` (a cudaStream_t, NULL = the
+** legacy stream): norm phase, device-wide bounded barrier, decision, update
+** phase, twin emission, and for fp8 segments a second barrier and the
+** quantising phase.  Replaces the reference sequence gpu_grad_sumsq -> host
+** sqrt/clip/skip -> gpu_adam_step_dev_bf16 (lang/lm_adam.c:466-493) and its two
+** host round trips.  Single-GPU form: the norm is this shard's alone.
+*/
+int	anni_optstep_step(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
+
+/*
+** The same step cut at its two global dependencies, for ZeRO-1: between the
+** calls the caller all-reduces small device buffers across ranks.
+**   anni_optstep_norm      local sum of squares -> reduce buffer {sumsq, nonfinite}
+**     [all-reduce SUM of anni_optstep_reduce_buffer(h): 2 doubles]
+**   anni_optstep_update    decision + AdamW + bf16 twins + per-tensor amax
+**     [all-reduce MAX of anni_optstep_amax_buffer(h): n_seg floats; fp8 only]
+**   anni_optstep_quantize  scale from amax, e4m3 twins of the fresh master
+*/
+int	anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
+int	anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
+int	anni_optstep_quantize(anni_optstep *h, void *stream);
+double	*anni_optstep_reduce_buffer(anni_optstep *h);	/* device double[2] */
+float	*anni_optstep_amax_buffer(anni_optstep *h);	/* device float[n_seg] */
+float	*anni_optstep_scale_buffer(anni_optstep *h);	/* device float[n_seg]: dequantisation scales */
+
+/* Blocks until `stream` has finished the queued steps, then copies the status. */
+int	anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *stream);
+
+/*
+** Dynamic loss scale kept on the device: a skipped step multiplies it by
+** `backoff`, `growth_interval` clean steps in a row multiply it by `growth`.
+** Steps that pass ANNI_STEP_DEV_LOSS_SCALE use grad_scale / loss_scale.  The
+** reference has no counterpart (its fp16 loss scaling was removed); scale <= 0
+** switches the state machine off.
+*/
+int	anni_optstep_loss_scale_init(anni_optstep *h, double scale, int growth_interval,
+		double growth, double backoff, double min_scale, double max_scale);
+
+/* Launch geometry in use (blocks of the persistent grid, threads per block). */
+int	anni_optstep_grid(anni_optstep *h, int *blocks, int *threads);
+
+/* Number of kernels this library has launched in this process (all entry points). */
+uint64_t anni_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

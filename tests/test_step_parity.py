@@ -1,0 +1,87 @@
+"""GPU parity: the CUDA step (through the C ABI) against the CPU oracle, same seeded inputs."""
+import numpy as np
+import pytest
+
+from anni_b200.capi import DT_BF16, DT_F32, SEG_TWIN_BF16, SEG_WD
+from anni_b200.engine import Segments, lm_segments, LM_SHAPES
+from parity_util import (bf16_bits_from_f32, check_step, make_inputs, run_gpu)
+
+pytestmark = pytest.mark.gpu
+
+HYP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
+
+
+def _oracle_step(oracle, segs, p, g, m, v, **kw):
+    a = [x.copy() for x in (p, g, m, v)]
+    info = oracle.step(*a, seg_off=segs.offsets if segs is not None else None,
+                       seg_flags=segs.flag_array if segs is not None else None, **kw)
+    return a, info
+
+
+@pytest.mark.parametrize("grad_dtype,state_dtype", [(DT_F32, DT_F32), (DT_BF16, DT_F32),
+                                                    (DT_BF16, DT_BF16), (DT_F32, DT_BF16)])
+@pytest.mark.parametrize("clip", [0.0, 1.0])
+@pytest.mark.parametrize("split", [False, True])
+def test_tiny_lm_step(oracle, grad_dtype, state_dtype, clip, split):
+    """The reference's unit-test LM (138,156 scalars, 27 tensors), wd on matrices only."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=1, grad_dtype=grad_dtype, state_dtype=state_dtype)
+    kw = dict(HYP, wd=0.1, clip=clip, grad_scale=1.0, t_before=999)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(segs, p, g, m, v, dict(HYP, wd=0.1, clip=clip, grad_scale=1.0, t=1000), split=split)
+    st = out["status"]
+    assert st.error == 0 and st.skipped == 0 and not info["skipped"]
+    assert abs(st.norm - info["norm"]) <= 1e-5 * info["norm"] + 1e-300
+    clipped = clip > 0 and info["norm"] > clip
+    res = check_step(out, rp, rm, rv, p, exact_moments=not clipped)
+    assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"]))      # twin = RNE(GPU master)
+    assert not out["g"].any()                                             # grads zeroed by the step
+    assert res["p_exact"] > 0.9
+
+
+def test_all_params_decay_matches_reference_layout(oracle):
+    """n_seg = 0: one implicit segment with decay everywhere, the reference kernels' behaviour."""
+    n = 70001          # odd size: exercises the element-wise tail
+    p, g, m, v = make_inputs(n, seed=2)
+    kw = dict(HYP, wd=0.1, clip=1.0, grad_scale=0.5, t_before=0)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, None, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(None, p, g, m, v, dict(HYP, wd=0.1, clip=1.0, grad_scale=0.5, t=1), n_arena=n)
+    assert abs(out["status"].norm - info["norm"]) <= 1e-5 * info["norm"]
+    check_step(out, rp, rm, rv, p, exact_moments=not (info["norm"] > 1.0))
+    assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"]))
+
+
+def test_unaligned_segment_boundaries(oracle):
+    """Tensor sizes that are not multiples of the vector width: boundaries fall inside vectors."""
+    segs = Segments()
+    for i, sz in enumerate([5, 4099, 1, 2048, 7777, 3, 12289]):
+        segs.add(f"t{i}", sz, (SEG_WD if i % 2 == 0 else 0) | SEG_TWIN_BF16)
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=3, grad_dtype=DT_BF16)
+    kw = dict(HYP, wd=0.1, clip=0.0, grad_scale=1.0 / 1024, t_before=10)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(segs, p, g, m, v, dict(HYP, wd=0.1, clip=0.0, grad_scale=1.0 / 1024, t=11))
+    check_step(out, rp, rm, rv, p, exact_moments=True)
+    assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"]))
+
+
+@pytest.mark.parametrize("bad", [np.inf, -np.inf, np.nan])
+@pytest.mark.parametrize("split", [False, True])
+def test_skip_step_on_nonfinite(oracle, bad, split):
+    """A single non-finite gradient: parameters, moments and twins untouched, grads zeroed."""
+    segs = lm_segments(**LM_SHAPES["tiny"])
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=4, grad_dtype=DT_BF16)
+    gf = (g.astype(np.uint32) << 16).view(np.float32).copy()
+    gf[n // 3] = bad
+    g = bf16_bits_from_f32(gf) if not np.isnan(bad) else g.copy()
+    if np.isnan(bad):
+        g[n // 3] = 0x7fc0
+    kw = dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t_before=5)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    assert info["skipped"]
+    out = run_gpu(segs, p, g, m, v, dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t=6), split=split)
+    assert out["status"].skipped == 1
+    assert np.array_equal(out["p"], p) and np.array_equal(out["m"], m) and np.array_equal(out["v"], v)
+    assert not out["g"].any() and not out["twin"].any()      # twin buffer never written
