@@ -1,0 +1,138 @@
+"""ZeRO-1 partitioning of the optimizer step over the GPUs of one node.
+
+The reference trainer is single-GPU (its README lists multi-GPU as an open item), so
+this layer has no counterpart there; parity is defined against the single-device CPU
+step applied to the REDUCED gradients.
+
+Layout: the packed arena (``lang/lm_adam.c:217-311`` of the reference: one running
+element offset per tensor) is padded to ``world * shard`` elements and cut into
+``world`` equal contiguous shards irrespective of tensor boundaries.  Every rank holds
+the full gradient arena (input of the reduce-scatter) and the full twin arena (output of
+the all-gather); rank r owns master / m / v of shard r only.  Per step::
+
+    reduce_scatter(sum)  bf16 or fp32 gradients      -> this rank's gradient shard
+    norm kernel          local sum of squares        -> {sumsq, nonfinite}
+    all_reduce(sum)      2 doubles                   -> global norm and skip flag
+    update kernel        decision + AdamW + bf16 twin + per-tensor amax
+    [all_reduce(max) of amax[n_seg]; quantise kernel]       (fp8 twins only)
+    all_gather           twins, in place inside the full twin arena
+
+``torch.distributed`` (NCCL over NVLink / NVSwitch) is the plumbing; the arithmetic is
+in ``libanni_b200.so``.  The collectives see only this process's own device memory.
+"""
+import torch
+import torch.distributed as dist
+
+from .capi import DT_BF16, DT_F32
+
+_TORCH_DT = {DT_F32: torch.float32, DT_BF16: torch.bfloat16}
+SHARD_ALIGN = 4096      # elements: keeps every shard base 16-byte aligned for all dtypes
+
+
+def shard_geometry(n_arena, world, align=SHARD_ALIGN):
+    """(shard elements incl. padding, [(offset, owned elements) per rank])."""
+    per = -(-int(n_arena) // world)
+    per = -(-per // align) * align
+    own = []
+    for r in range(world):
+        off = min(r * per, n_arena)
+        own.append((r * per, max(0, min(per, n_arena - off)) if r * per < n_arena else 0))
+    return per, own
+
+
+class Zero1:
+    """Host-side driver of the sharded step.
+
+    ``make_stepper(shard_off, shard_n)`` builds the object that steps one shard; by
+    default that is the CUDA engine (:class:`anni_b200.engine.OptStep`).  The object must
+    offer ``allocate / bind``-style buffers (see ``_Buffers``) and the calls ``norm``,
+    ``update``, ``quantize``, ``reduce_tensor``, ``amax_tensor``, ``has_fp8``.
+    """
+
+    def __init__(self, segments, *, grad_dtype=DT_BF16, state_dtype=DT_F32, group=None,
+                 device=None, make_stepper=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.segments = segments
+        self.n_arena = segments.n
+        self.per, own = shard_geometry(self.n_arena, self.world)
+        self.shard_off, self.shard_n = own[self.rank]
+        self.padded = self.per * self.world
+        if make_stepper is None:
+            from .engine import OptStep
+            dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+
+            def make_stepper(off, n):
+                return OptStep(segments, grad_dtype=grad_dtype, state_dtype=state_dtype,
+                               shard_off=off, shard_n=n, device=dev)
+            self.device = dev
+        else:
+            self.device = torch.device("cpu") if device is None else device
+        # an empty shard still takes part in every collective; it sits at the arena end
+        self.eng = make_stepper(min(self.shard_off, self.n_arena), self.shard_n)
+        gdt, sdt, dev = _TORCH_DT[grad_dtype], _TORCH_DT[state_dtype], self.device
+        self.grad_full = torch.zeros(self.padded, dtype=gdt, device=dev)
+        self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
+        self.twin8_full = (torch.zeros(self.padded, dtype=torch.uint8, device=dev)
+                           if self.eng.has_fp8 else None)
+        lo, hi = self.rank * self.per, (self.rank + 1) * self.per
+        self.master = torch.zeros(self.per, dtype=torch.float32, device=dev)
+        self.m = torch.zeros(self.per, dtype=sdt, device=dev)
+        self.v = torch.zeros(self.per, dtype=sdt, device=dev)
+        # with one rank the reduce-scatter is the identity: step the arena in place
+        self.grad_shard = (self.grad_full[lo:hi] if self.world == 1
+                           else torch.zeros(self.per, dtype=gdt, device=dev))
+        self.twin_shard = self.twin_full[lo:hi]
+        self.twin8_shard = self.twin8_full[lo:hi] if self.twin8_full is not None else None
+        self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard,
+                      self.twin8_shard)
+        self.timing = None
+
+    # -- state in / out (arena order, full arrays; used by tests and checkpoints) -------
+    def load_shard_from_full(self, master_full, m_full, v_full):
+        lo, n = self.shard_off, self.shard_n
+        if n:
+            self.master[:n].copy_(master_full[lo:lo + n])
+            self.m[:n].copy_(m_full[lo:lo + n])
+            self.v[:n].copy_(v_full[lo:lo + n])
+
+    def gather_full(self, shard):
+        """All ranks' shards of a per-rank buffer, concatenated in arena order (unpadded)."""
+        if self.world == 1:
+            return shard[:self.n_arena].clone()
+        out = torch.empty(self.padded, dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(out, shard.contiguous(), group=self.group)
+        return out[:self.n_arena]
+
+    # -- the step ------------------------------------------------------------------------
+    def step(self, hp, record=None):
+        """One sharded step.  ``record`` (optional) is called with a phase name after each
+        phase has been queued, so a caller can drop timing events between them."""
+        mark = record if record is not None else (lambda name: None)
+        if self.world == 1 and hasattr(self.eng, "step"):
+            self.eng.step(hp)           # nothing to exchange: the single cooperative launch
+            mark("step")
+            return
+        if self.world > 1:
+            dist.reduce_scatter_tensor(self.grad_shard, self.grad_full, op=dist.ReduceOp.SUM,
+                                       group=self.group)
+        mark("reduce_scatter")
+        self.eng.norm(hp)
+        if self.world > 1:
+            dist.all_reduce(self.eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)
+        mark("norm")
+        self.eng.update(hp)
+        if self.eng.has_fp8:
+            if self.world > 1:
+                dist.all_reduce(self.eng.amax_tensor(), op=dist.ReduceOp.MAX, group=self.group)
+            self.eng.quantize()
+        mark("update")
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.twin_full, self.twin_shard, group=self.group)
+            if self.twin8_full is not None:
+                dist.all_gather_into_tensor(self.twin8_full, self.twin8_shard, group=self.group)
+        mark("all_gather")
+
+    def status(self):
+        return self.eng.status()
