@@ -85,3 +85,35 @@ def test_skip_step_on_nonfinite(oracle, bad, split):
     assert out["status"].skipped == 1
     assert np.array_equal(out["p"], p) and np.array_equal(out["m"], m) and np.array_equal(out["v"], v)
     assert not out["g"].any() and not out["twin"].any()      # twin buffer never written
+
+
+@pytest.mark.parametrize("split", [False, True])
+def test_fp8_twins_per_tensor_scale(oracle, split):
+    """e4m3 twins of the block matrices: amax, scale and codes are those of the oracle's
+    restatement of the reference quantiser applied to the GPU master (bit-exact); vectors,
+    head and embedding keep bf16 twins."""
+    from anni_b200.capi import SEG_TWIN_FP8
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin="fp8")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=5, grad_dtype=DT_BF16)
+    p[segs.slice_of("blk0.wq")] *= 37.0            # tensors with different ranges
+    p[segs.slice_of("blk1.w2")] *= 1e-3
+    kw = dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t_before=99)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(segs, p, g, m, v, dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t=100), split=split)
+    check_step(out, rp, rm, rv, p, exact_moments=not info["norm"] > 1.0)
+    off = segs.offsets
+    n_fp8 = 0
+    for i, name in enumerate(segs.names):
+        sl = slice(int(off[i]), int(off[i + 1]))
+        if segs.flags[i] & SEG_TWIN_FP8:
+            amax, scale, q = oracle.fp8_quant(out["p"][sl])
+            assert np.float32(out["amax"][i]) == np.float32(amax), name
+            assert np.float32(out["scale"][i]) == np.float32(scale), name
+            assert np.array_equal(out["twin8"][sl], q), name
+            assert not out["twin"][sl].any()
+            n_fp8 += 1
+        else:
+            assert np.array_equal(out["twin"][sl], bf16_bits_from_f32(out["p"][sl])), name
+            assert not out["twin8"][sl].any()
+    assert n_fp8 == 12
