@@ -14,6 +14,7 @@ DT_F32, DT_BF16 = 0, 1
 SEG_WD, SEG_TWIN_BF16, SEG_TWIN_FP8 = 1, 2, 4
 STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE = 1, 2, 4
 OK, E_ARG, E_CUDA, E_BARRIER_TIMEOUT, E_NOMEM, E_LIMIT = 0, -1, -2, -3, -4, -5
+NOALLOC_MAX_SEG = 1024
 
 
 class Config(C.Structure):
@@ -72,6 +73,10 @@ def lib():
     L.anni_optstep_loss_scale_init.argtypes = [vp, d, i, d, d, d, d]
     L.anni_optstep_grid.restype = i
     L.anni_optstep_grid.argtypes = [vp, C.POINTER(i), C.POINTER(i)]
+    L.anni_optstep_step_noalloc.restype = i
+    L.anni_optstep_step_noalloc.argtypes = [C.POINTER(Config), C.POINTER(Buffers), C.POINTER(Hyper), vp, vp]
+    L.anni_optstep_status_noalloc.restype = i
+    L.anni_optstep_status_noalloc.argtypes = [C.POINTER(Status), vp]
     L.anni_kernel_launches.restype = C.c_uint64
     L.anni_kernel_launches.argtypes = []
     _LIB = L

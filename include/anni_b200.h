@@ -170,6 +170,29 @@ int	anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *st
 int	anni_optstep_loss_scale_init(anni_optstep *h, double scale, int growth_interval,
 		double growth, double backoff, double min_scale, double max_scale);
 
+/*
+** The whole step (same kernel and arithmetic as anni_optstep_step) for callers
+** that cannot allocate device memory: no engine is created, and the working
+** memory the step needs (barrier counters, per-block partial sums, the device
+** copy of the tensor table, per-tensor amax/scale) is a fixed array built into
+** the library, present on every GPU that loads it.  No counterpart in the
+** reference.  Limits and rules:
+**   - at most ANNI_NOALLOC_MAX_SEG tensors in cfg->seg_off / seg_flags; more is
+**     refused with ANNI_E_LIMIT before anything is queued;
+**   - all calls on one device share that array: queue them one after another on
+**     a single stream; calls that overlap on the GPU corrupt each other;
+**   - the first call on a device resolves the array's device address: make it
+**     during start-up, before any stream capture on that device;
+**   - ANNI_STEP_DEV_LOSS_SCALE is not available (fold 1/loss_scale into grad_scale).
+** cfg, buf, hp as for create / bind / step.  seg_scale_out (device, n_seg floats,
+** may be NULL) receives the e4m3 dequantisation scales when fp8 twins are asked for.
+*/
+#define ANNI_NOALLOC_MAX_SEG	1024
+int	anni_optstep_step_noalloc(const anni_optstep_config *cfg, const anni_optstep_buffers *buf,
+		const anni_optstep_hyper *hp, float *seg_scale_out, void *stream);
+/* Status of the last no-alloc step on the current device (synchronises `stream`). */
+int	anni_optstep_status_noalloc(anni_optstep_status *out, void *stream);
+
 /* Launch geometry in use (blocks of the persistent grid, threads per block). */
 int	anni_optstep_grid(anni_optstep *h, int *blocks, int *threads);
 
