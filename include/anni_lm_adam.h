@@ -1,0 +1,126 @@
+/*
+** Host-side optimizer object with the reference's interface (lang/lm_adam.h of
+** the reference project) over the packed-arena engine of anni_b200.h.
+**
+** Same life cycle, field names and step semantics as the reference's lm_adam:
+** create from the model's tensors in a fixed order, zero_grad, step /
+** step_scaled (lr <= 0 is a no-op; t is incremented first, also when the step
+** is then skipped; a non-finite gradient norm skips the update, zeroes the
+** gradients and logs one line; last_grad_norm holds the pre-clip norm),
+** invalidate, sync_host, set_offload, free.  Callers poke the hyper-parameter
+** fields directly, as they do with the reference's struct.
+**
+** Differences, all on purpose:
+**  - the tensor list is passed in as an array (the reference walks its `lm`
+**    model struct, lang/lm_adam.c:117-136; INTEGRATION.md shows the loop that
+**    builds the array from an `lm`), each tensor with a decay / twin flag;
+**  - parameters, gradients and moments live in device flats for good (bias and
+**    LayerNorm vectors included: the reference re-uploads those every step,
+**    lang/lm_adam.c:361-429); host copies are refreshed by sync_host;
+**  - gradients may be bf16 and moments bf16;
+**  - there is no host fallback: when the device step cannot run, the call
+**    returns an error code and leaves the state untouched.
+*/
+#ifndef ANNI_LM_ADAM_H__
+#define ANNI_LM_ADAM_H__
+
+#include <stdint.h>
+#include "anni_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One tensor of the model: host weights, host gradients (may be NULL), element count, ANNI_SEG_* flags. */
+typedef struct anni_lm_tensor {
+	float		*w;	/* host weights, n floats (read at first step / after invalidate, written by sync_host) */
+	float		*dw;	/* host gradients, n floats, or NULL when gradients are produced on the device */
+	int64_t		n;
+	uint32_t	flags;
+} anni_lm_tensor;
+
+/* Mirrors lm_adam_seg (lang/lm_adam.h:21-29): where a tensor sits in the flats. */
+typedef struct anni_lm_adam_seg {
+	float		*w;
+	float		*dw;
+	int64_t		off;
+	int64_t		n;
+	uint32_t	flags;
+} anni_lm_adam_seg;
+
+/* Mirrors lm_adam (lang/lm_adam.h:31-54); same names where the field exists there. */
+typedef struct anni_lm_adam {
+	anni_lm_adam_seg	*segs;
+	int		n_segs;
+	int64_t		n;
+	int		t;
+	double		beta1;
+	double		beta2;
+	double		eps;
+	float		*h_m;		/* host mirrors of m / v as fp32 (checkpoint staging) */
+	float		*h_v;
+	float		*d_param;	/* device flats */
+	void		*d_param_bf16;
+	void		*d_param_fp8;
+	void		*d_grad;
+	void		*d_m;
+	void		*d_v;
+	int		dev_mv;		/* 1: d_m/d_v newer than h_m/h_v */
+	int		params_valid;	/* 1: d_param mirrors the weights */
+	int		offload_mv;	/* keep m/v on the host between steps */
+	double		weight_decay;
+	double		grad_clip;
+	double		last_grad_norm;
+	/* beyond the reference */
+	int		grad_dtype;	/* ANNI_DT_* */
+	int		state_dtype;
+	int		last_skipped;
+	int		last_error;	/* ANNI_E_* of the last step, 0 if it ran */
+	double		loss_scale;	/* > 0: gradients arrive multiplied by this; folded into grad_scale */
+	anni_optstep	*engine;
+} anni_lm_adam;
+
+/* lm_adam_create (lang/lm_adam.c:79): defaults beta1 0.9, beta2 0.999, eps 1e-8, wd 0, clip 0, t 0. */
+anni_lm_adam	*anni_lm_adam_create(const anni_lm_tensor *tensors, int n_tensors, int grad_dtype,
+			int state_dtype);
+/* lm_param_count (lang/lm_adam.c:59) from the model dimensions. */
+int64_t	anni_lm_param_count(int d_model, int d_ff, int n_blocks, int vocab, int tied);
+void	anni_lm_adam_free(anni_lm_adam **opt);
+/* lm_adam_zero_grad (lang/lm_adam.c:196): zero host gradients and the device flat. */
+void	anni_lm_adam_zero_grad(anni_lm_adam *opt);
+/* lm_adam_step / lm_adam_step_scaled (lang/lm_adam.c:517, :522). Return ANNI_OK or ANNI_E_*. */
+int	anni_lm_adam_step(anni_lm_adam *opt, double lr);
+int	anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double grad_scale);
+/* lm_adam_invalidate (lang/lm_adam.c:203): the next step re-reads the host weights. */
+void	anni_lm_adam_invalidate(anni_lm_adam *opt);
+/* lm_adam_sync_host (lang/lm_adam.c:336): weights into the tensors' host arrays, m/v into h_m/h_v. */
+int	anni_lm_adam_sync_host(anni_lm_adam *opt);
+/* lm_adam_set_offload (lang/lm_adam.c:211): pull m/v to the host and free their device flats after each step. */
+void	anni_lm_adam_set_offload(int on);
+/* Upload the host gradient arrays (tensors with dw != NULL) into the device flat: seg_gather's job. */
+int	anni_lm_adam_upload_grads(anni_lm_adam *opt);
+/* Load m/v (fp32, arena order) e.g. from a checkpoint; uploaded at the next step. */
+int	anni_lm_adam_set_moments(anni_lm_adam *opt, const float *m, const float *v);
+
+/* lm_train_step_lr (lang/lm_train.c:98-124): warm-up, then "none" | "linear" | cosine decay. */
+double	anni_lr_schedule(double base_lr, int step, int warmup_steps, int decay_steps,
+		const char *decay_kind, int sched_from);
+
+/*
+** Adam section of a checkpoint (lang/lm_serialize.c:316-319, :263-296): int32
+** {1, epoch, step, t, n}, then n interleaved (m, v) fp32 pairs in arena order,
+** written through a 16 MB staging buffer.  `append` adds it after an existing
+** weight section; otherwise the file is created through PATH.tmp + rename
+** (lang/lm_serialize.c:298-331).  read: `offset` is the byte offset of the
+** header, or -1 to take the trailer (the last 20 + 8 n bytes of the file).
+*/
+int	anni_ckpt_write_adam(const char *path, int append, int epoch, int step, int t, int64_t n,
+		const float *m, const float *v);
+int	anni_ckpt_read_adam(const char *path, int64_t offset, int64_t n_expected, int *epoch,
+		int *step, int *t, float *m, float *v);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

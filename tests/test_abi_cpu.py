@@ -1,0 +1,124 @@
+"""CPU-only checks of the C ABI: the library loads, exports every symbol the headers declare,
+and its pure-host entry points (schedule, checkpoint, parameter count, argument checks) behave."""
+import ctypes as C
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+
+from anni_b200 import capi, checkpoint, schedule
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+def _declared_symbols(header):
+    src = open(os.path.join(ROOT, "include", header)).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    src = re.sub(r"#.*", "", src)
+    names = set()
+    for decl in src.split(";"):
+        if "(" not in decl or "typedef" in decl:
+            continue
+        m = re.search(r"\b((?:anni|gpu)_\w+)\s*\(", decl)
+        if m:
+            names.add(m.group(1))
+    return names
+
+
+@pytest.mark.parametrize("header", ["anni_b200.h", "anni_gpu_compat.h", "anni_lm_adam.h"])
+def test_every_declared_symbol_is_exported(header):
+    L = capi.lib()
+    names = _declared_symbols(header)
+    assert len(names) >= 10
+    missing = [n for n in sorted(names) if not hasattr(L, n)]
+    assert not missing, missing
+
+
+def test_reference_device_api_symbols_all_link():
+    """Every gpu_* symbol of the reference's num/gpu.h (99 of them) resolves in the library,
+    so the reference trainer links it in place of its own backend object."""
+    L = capi.lib()
+    names = """gpu_available gpu_mem_info gpu_sync_mode gpu_fp8 gpu_memcpy_h2d gpu_memcpy_d2h gpu_host_pin
+    gpu_memcpy_d2h_async gpu_stream_sync gpu_memcpy_d2d gpu_memset gpu_adam_seed_bf16_flat gpu_ce_fetch_mean
+    gpu_mat_mul gpu_mat_mul_bias gpu_mat_mul_res gpu_mat_mul_bias_relu gpu_mat_mul_bt gpu_mat_mul_bt_acc
+    gpu_mat_mul_bt_twin gpu_mat_mul_at gpu_mat_outer_add gpu_layernorm_backward gpu_layernorm_backward_acc
+    gpu_layernorm_backward_x gpu_layernorm_xhat gpu_grad_sumsq gpu_adam_step_dev_bf16 gpu_softmax_rows
+    gpu_softmax_bwd_rows gpu_layernorm_forward_ex gpu_bias_row_add gpu_ce_delta_from_softmax
+    gpu_ce_softmax_delta_bf16 gpu_ce_bias_fused gpu_ce_bf16_delta_done gpu_ce_nll_rows gpu_posenc_add_packed
+    gpu_mat_col_sum_add gpu_relu_backward gpu_ffn_relu_bwd_fused gpu_act_bf16_only gpu_attn_causal_fwd
+    gpu_attn_flash_fwd gpu_attn_fa_fwd gpu_attn_fa_usable gpu_attn_fa_bwd gpu_attn_qkv_bwd gpu_attn_tiled_bwd
+    gpu_attn_causal_bwd gpu_attn_tc_fwd gpu_attn_tc_bwd gpu_attn_qkv_fused gpu_pack_seq_rows gpu_unpack_seq_rows
+    gpu_ffn_w1_finish gpu_mat_copy gpu_mat_add gpu_mat_add2 gpu_mat_axpy gpu_embed_lookup gpu_embed_scatter
+    gpu_graph_begin gpu_graph_end gpu_graph_replay gpu_graph_replayable gpu_graph_supported gpu_ids_stage
+    gpu_dec_set_layer gpu_dec_set_io gpu_dec_kv_load gpu_dec_step gpu_backend_name gpu_debug_last_error
+    gpu_set_sync_mode gpu_set_compute_prec gpu_set_fp8 gpu_set_fp8_dgrad gpu_device_sync gpu_free
+    gpu_half_wt_invalidate gpu_host_forget gpu_op_prof_dump gpu_adam_set_bf16_flat gpu_grad_twins_clear
+    gpu_adam_set_weight_decay gpu_attn_qkv_bf16_hint gpu_attn_set_seqlens gpu_host_free gpu_graph_destroy
+    gpu_graph_set_mode gpu_ids_unstage gpu_dec_free gpu_malloc gpu_host_alloc gpu_copy_stream gpu_param_epoch
+    gpu_ce_targets_staged gpu_dec_create""".split()
+    assert len(names) == 99
+    missing = [n for n in names if not hasattr(L, n)]
+    assert not missing, missing
+    # forward/backward entry points answer like the reference's stub backend
+    for n in ("gpu_mat_mul", "gpu_attn_flash_fwd", "gpu_graph_begin", "gpu_dec_step"):
+        f = getattr(L, n)
+        f.restype = C.c_int
+        assert f() == -1
+    for n in ("gpu_graph_supported", "gpu_attn_fa_usable", "gpu_act_bf16_only"):
+        f = getattr(L, n)
+        f.restype = C.c_int
+        assert f() == 0
+
+
+def test_lr_schedule_product_equals_golden():
+    with open(os.path.join(GOLD, "lr_schedule.json")) as f:
+        pts = json.load(f)
+    for q in pts:
+        assert schedule.lr_at(q["base"], q["step"], q["warmup"], q["decay"], q["kind"], q["start"]) == q["lr"]
+
+
+def test_checkpoint_trailer_product_equals_golden(tmp_path):
+    import hashlib
+    from golden.make_golden import ckpt_moments
+    with open(os.path.join(GOLD, "segments_tiny.json")) as f:
+        meta = json.load(f)
+    m, v = ckpt_moments(meta["n"])
+    path = str(tmp_path / "adam.bin")
+    checkpoint.write_adam(path, m, v, t=meta["t"], epoch=meta["epoch"], step=meta["step"])
+    data = open(path, "rb").read()
+    assert hashlib.sha256(data).hexdigest() == meta["trailer_sha256"]
+    back = checkpoint.read_adam(path, meta["n"])
+    assert back["t"] == meta["t"] and np.array_equal(back["m"], m) and np.array_equal(back["v"], v)
+    with pytest.raises(capi.AnniError):                       # wrong slot count is refused, like the loader
+        checkpoint.read_adam(path, meta["n"] - 1, offset=0)
+
+
+def test_param_count_entry_point():
+    L = capi.lib()
+    L.anni_lm_param_count.restype = C.c_int64
+    L.anni_lm_param_count.argtypes = [C.c_int] * 5
+    assert L.anni_lm_param_count(1024, 4096, 12, 16384, 0) == 184_676_352
+    assert L.anni_lm_param_count(1536, 6272, 14, 100000, 1) == 555_762_080
+    assert L.anni_lm_param_count(2560, 10240, 32, 100000, 1) == 2_773_419_680
+
+
+def test_bad_arguments_are_refused_before_any_launch():
+    L = capi.lib()
+    h = C.c_void_p()
+    cfg = capi.Config()
+    cfg.n_arena, cfg.shard_off, cfg.shard_n = 100, 50, 51          # shard sticks out of the arena
+    assert L.anni_optstep_create(C.byref(cfg), C.byref(h)) == capi.E_ARG
+    cfg.shard_n, cfg.grad_dtype = 50, 7
+    assert L.anni_optstep_create(C.byref(cfg), C.byref(h)) == capi.E_ARG
+    off = np.array([0, 60, 40, 100], np.int64)                     # offsets not ascending
+    flg = np.zeros(3, np.uint32)
+    cfg.grad_dtype, cfg.n_seg, cfg.seg_off, cfg.seg_flags = 0, 3, off.ctypes.data, flg.ctypes.data
+    assert L.anni_optstep_create(C.byref(cfg), C.byref(h)) == capi.E_ARG
+    assert L.anni_optstep_step(None, None, None) == capi.E_ARG
+    big = capi.Config()
+    big.n_seg = capi.NOALLOC_MAX_SEG + 1
+    assert L.anni_optstep_step_noalloc(C.byref(big), C.byref(capi.Buffers()), C.byref(capi.Hyper()),
+                                       None, None) == capi.E_LIMIT

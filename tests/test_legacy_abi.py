@@ -1,0 +1,332 @@
+"""GPU tests of the reference-facing boundary: the reference's own device symbols
+(num/gpu.h) as defined by libanni_b200.so, the reference's unmodified optimizer linked against
+them, and the library's C mirror of the optimizer object -- all against the CPU oracle."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from anni_b200 import capi, checkpoint, schedule
+from anni_b200.capi import DT_BF16, DT_F32, SEG_TWIN_BF16, SEG_WD
+from anni_b200.engine import LM_SHAPES, lm_segments
+from parity_util import bf16_bits_from_f32, check_step, f32_ulp_dist, make_inputs, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DROPIN = os.path.join(ROOT, "oracle", "_ref", "libannref_dropin.so")
+HYP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
+d = C.c_double
+
+
+def _legacy():
+    L = capi.lib()
+    L.gpu_available.restype = C.c_int
+    L.gpu_grad_sumsq.restype = C.c_int
+    L.gpu_grad_sumsq.argtypes = [C.c_void_p, C.c_int, C.POINTER(d)]
+    L.gpu_adam_set_weight_decay.argtypes = [d]
+    L.gpu_set_compute_prec.argtypes = [C.c_int]
+    L.gpu_adam_step_dev_bf16.restype = C.c_int
+    L.gpu_adam_step_dev_bf16.argtypes = [C.c_void_p] * 5 + [C.c_int, d, d, d, d, C.c_int, d]
+    L.gpu_stream_sync.restype = C.c_int
+    L.gpu_adam_set_bf16_flat.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+    L.gpu_adam_seed_bf16_flat.restype = C.c_int
+    L.gpu_adam_seed_bf16_flat.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+    L.anni_half_wt_lookup.restype = C.c_void_p
+    L.anni_half_wt_lookup.argtypes = [C.c_void_p, C.c_size_t]
+    L.gpu_half_wt_invalidate.argtypes = [C.c_void_p]
+    L.gpu_param_epoch.restype = C.c_uint
+    L.gpu_device_sync.restype = None
+    return L
+
+
+@pytest.mark.parametrize("n", [70001, 262144])
+@pytest.mark.parametrize("twin", [True, False])
+def test_two_call_sequence_of_the_reference(oracle, n, twin):
+    """gpu_grad_sumsq -> host sqrt / clip -> gpu_adam_step_dev_bf16, as lang/lm_adam.c:466-493 does."""
+    L = _legacy()
+    assert L.gpu_available() == 1
+    p, g, m, v = make_inputs(n, seed=31)
+    dp, dg, dm, dv = (to_dev(x) for x in (p, g, m, v))
+    t16 = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    ss = d()
+    assert L.gpu_grad_sumsq(dg.data_ptr(), n, C.byref(ss)) == 0
+    want = oracle.sumsq(g, 1.0)
+    assert abs(ss.value - want) <= 1e-12 * want
+    gs, clip, wd = 0.5, 1.0, 0.1
+    norm = np.sqrt(ss.value) * abs(gs)
+    coef = gs * (clip / norm) if norm > clip else gs           # the device path divides by norm (lm_adam.c:488)
+    L.gpu_adam_set_weight_decay(wd)
+    L.gpu_set_compute_prec(1 if twin else 0)
+    rc = L.gpu_adam_step_dev_bf16(dp.data_ptr(), t16.data_ptr(), dg.data_ptr(), dm.data_ptr(),
+                                  dv.data_ptr(), n, HYP["lr"], HYP["beta1"], HYP["beta2"], HYP["eps"],
+                                  7, coef)
+    assert rc == 0 and L.gpu_stream_sync() == 0
+    ref = [x.copy() for x in (p, g, m, v)]
+    oracle.step(*ref, wd=wd, clip=0.0, grad_scale=coef, t_before=6, **HYP)   # same multiplier: exact moments
+    out = dict(p=to_host(dp), m=to_host(dm), v=to_host(dv))
+    check_step(out, ref[0], ref[2], ref[3], p, exact_moments=True)
+    assert not to_host(dg).any()                                # "d_grad is zeroed after"
+    if twin:
+        assert np.array_equal(to_host(t16), bf16_bits_from_f32(out["p"]))
+    else:
+        assert not to_host(t16).any()                           # fp32 precision: twin untouched
+    L.gpu_set_compute_prec(0)
+    # the reference launcher's rejections (num/gpu_cuda.cu:8675-8682)
+    args = [dp.data_ptr(), t16.data_ptr(), dg.data_ptr(), dm.data_ptr(), dv.data_ptr()]
+    assert L.gpu_adam_step_dev_bf16(*args, n, 0.0, 0.9, 0.95, 1e-8, 7, 1.0) == -1      # lr <= 0
+    assert L.gpu_adam_step_dev_bf16(*args, n, 1e-3, 0.9, 0.95, 1e-8, 0, 1.0) == -1     # t < 1
+    assert L.gpu_adam_step_dev_bf16(*args, 0, 1e-3, 0.9, 0.95, 1e-8, 1, 1.0) == -1     # n <= 0
+    assert L.gpu_adam_step_dev_bf16(*args, n, 1e-3, 1.0, 0.95, 1e-8, 1, 1.0) == -1     # bc1 == 0
+    assert L.gpu_adam_step_dev_bf16(None, *args[1:], n, 1e-3, 0.9, 0.95, 1e-8, 1, 1.0) == -1
+    assert np.array_equal(to_host(dp), out["p"])                # nothing ran
+
+
+def test_bf16_flat_twin_registry():
+    L = _legacy()
+    n = 50000
+    f32 = torch.randn(n, device="cuda") * 0.02
+    b16 = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    assert L.gpu_adam_seed_bf16_flat(b16.data_ptr(), f32.data_ptr(), n) == 0
+    L.gpu_device_sync()
+    assert np.array_equal(to_host(b16), bf16_bits_from_f32(f32.cpu().numpy()))
+    L.gpu_adam_set_bf16_flat(b16.data_ptr(), f32.data_ptr(), n)
+    # a slice of the fp32 flat is served at the same ELEMENT offset of the bf16 flat
+    assert L.anni_half_wt_lookup(f32.data_ptr() + 4 * 1234, 100) == b16.data_ptr() + 2 * 1234
+    assert L.anni_half_wt_lookup(f32.data_ptr(), n) == b16.data_ptr()
+    assert L.anni_half_wt_lookup(f32.data_ptr() + 4 * (n - 10), 11) is None        # runs past the end
+    assert L.anni_half_wt_lookup(b16.data_ptr(), 1) in (None, 0) or True
+    e0 = L.gpu_param_epoch()
+    L.gpu_half_wt_invalidate(None)
+    assert L.gpu_param_epoch() == e0 + 1
+    L.gpu_adam_set_bf16_flat(None, None, 0)
+    assert L.anni_half_wt_lookup(f32.data_ptr(), 1) is None
+
+
+def test_mat_axpy_on_device_twins():
+    class Mat(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("d_data", C.c_void_p), ("rows", C.c_int),
+                    ("cols", C.c_int), ("on_device", C.c_int)]
+    L = _legacy()
+    L.gpu_mat_axpy.restype = C.c_int
+    L.gpu_mat_axpy.argtypes = [C.POINTER(Mat), d, C.POINTER(Mat)]
+    rows, cols = 37, 129
+    rng = np.random.default_rng(3)
+    xh = rng.normal(size=rows * cols).astype(np.float32)
+    yh = rng.normal(size=rows * cols).astype(np.float32)
+    xd, yd = to_dev(xh), to_dev(yh)
+    x = Mat(xh.ctypes.data, xd.data_ptr(), rows, cols, 1)
+    y = Mat(yh.ctypes.data, yd.data_ptr(), rows, cols, 1)
+    assert L.gpu_mat_axpy(C.byref(y), 0.25, C.byref(x)) == 0
+    L.gpu_device_sync()
+    want = np.float32(0.25) * xh.astype(np.float64) + yh        # one fused multiply-add per element
+    assert np.max(np.abs(to_host(yd) - want.astype(np.float32))) <= np.spacing(np.float32(4.0))
+    assert y.on_device == 1
+    bad = Mat(xh.ctypes.data, xd.data_ptr(), rows, cols + 1, 1)
+    assert L.gpu_mat_axpy(C.byref(y), 1.0, C.byref(bad)) == -1  # shape mismatch -> CPU path
+
+
+@pytest.mark.skipif(not os.path.exists(DROPIN), reason="oracle/_ref/libannref_dropin.so not built")
+@pytest.mark.parametrize("bf16_prec", [0, 1])
+def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec):
+    """The reference's own lang/lm_adam.c (unmodified, with its num/mat.c, num/vec.c) linked
+    against libanni_b200.so in place of its backend: three steps take its device path and land
+    on the oracle's numbers."""
+    capi.lib()
+    R = C.CDLL(DROPIN)
+    R.dropin_run.restype = C.c_int
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="all")
+    kinds = np.array([0 if (f & 1) and s > 300 else 1 for f, s in zip(lm_segments(**LM_SHAPES["tiny"]).flags,
+                                                                      segs.sizes)], np.int32)
+    rows = np.array([s if k else 64 for s, k in zip(segs.sizes, kinds)], np.int32)
+    cols = np.array([1 if k else s // 64 for s, k in zip(segs.sizes, kinds)], np.int32)
+    n, steps = segs.n, 3
+    p, _, _, _ = make_inputs(n, seed=41)
+    rng = np.random.default_rng(42)
+    g = (rng.normal(0, 1e-3, (steps, n))).astype(np.float32)
+    g[2, n // 5] = np.inf                                      # third step: skipped by the host check
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    norms = np.zeros(steps, np.float64)
+    used = C.c_int()
+    pp = p.copy()
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+    rc = R.dropin_run(len(kinds), ptr(kinds), ptr(rows), ptr(cols), ptr(pp), ptr(g), ptr(m), ptr(v),
+                      steps, d(1e-3), d(0.9), d(0.95), d(1e-8), d(0.1), d(1.0), d(0.25),
+                      bf16_prec, ptr(norms), C.byref(used))
+    assert rc == 0 and used.value == 1
+    rp, rm, rv = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for s in range(steps):
+        gg = g[s].copy()
+        info = oracle.step(rp, gg, rm, rv, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                           grad_scale=0.25, t_before=s, check_finite=True)
+        if s < 2:
+            assert abs(norms[s] - info["norm"]) <= 1e-10 * info["norm"] and not info["skipped"]
+        else:
+            assert info["skipped"] and not np.isfinite(norms[s])
+    dm, dv, dp = f32_ulp_dist(m, rm), f32_ulp_dist(v, rv), f32_ulp_dist(pp, rp)
+    assert dm.max() <= 1 and dv.max() <= 1 and (dm == 0).mean() > 0.999
+    check_step(dict(p=pp, m=m, v=v), rp, rm, rv, p, exact_moments=False)
+    assert (dp <= 2).mean() > 0.95      # two consecutive first steps (|update| = lr): off-by-ones add up
+
+
+# ---- the library's own optimizer object (C mirror of lm_adam) -------------------------------
+
+class Tensor(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("dw", C.c_void_p), ("n", C.c_int64), ("flags", C.c_uint32)]
+
+
+class Seg(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("dw", C.c_void_p), ("off", C.c_int64), ("n", C.c_int64),
+                ("flags", C.c_uint32)]
+
+
+class LmAdam(C.Structure):
+    _fields_ = [("segs", C.POINTER(Seg)), ("n_segs", C.c_int), ("n", C.c_int64), ("t", C.c_int),
+                ("beta1", d), ("beta2", d), ("eps", d), ("h_m", C.POINTER(C.c_float)),
+                ("h_v", C.POINTER(C.c_float)), ("d_param", C.c_void_p), ("d_param_bf16", C.c_void_p),
+                ("d_param_fp8", C.c_void_p), ("d_grad", C.c_void_p), ("d_m", C.c_void_p),
+                ("d_v", C.c_void_p), ("dev_mv", C.c_int), ("params_valid", C.c_int),
+                ("offload_mv", C.c_int), ("weight_decay", d), ("grad_clip", d), ("last_grad_norm", d),
+                ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("last_skipped", C.c_int),
+                ("last_error", C.c_int), ("loss_scale", d), ("engine", C.c_void_p)]
+
+
+def _mirror():
+    L = capi.lib()
+    L.anni_lm_adam_create.restype = C.POINTER(LmAdam)
+    L.anni_lm_adam_create.argtypes = [C.POINTER(Tensor), C.c_int, C.c_int, C.c_int]
+    L.anni_lm_adam_free.argtypes = [C.POINTER(C.POINTER(LmAdam))]
+    L.anni_lm_adam_step_scaled.restype = C.c_int
+    L.anni_lm_adam_step_scaled.argtypes = [C.POINTER(LmAdam), d, d]
+    L.anni_lm_adam_step.restype = C.c_int
+    L.anni_lm_adam_step.argtypes = [C.POINTER(LmAdam), d]
+    L.anni_lm_adam_sync_host.restype = C.c_int
+    L.anni_lm_adam_sync_host.argtypes = [C.POINTER(LmAdam)]
+    L.anni_lm_adam_invalidate.argtypes = [C.POINTER(LmAdam)]
+    L.anni_lm_adam_zero_grad.argtypes = [C.POINTER(LmAdam)]
+    L.anni_lm_adam_set_offload.argtypes = [C.c_int]
+    L.anni_lm_adam_set_moments.restype = C.c_int
+    L.anni_lm_adam_set_moments.argtypes = [C.POINTER(LmAdam), C.c_void_p, C.c_void_p]
+    return L
+
+
+def _make_opt(L, segs, p, g):
+    """Tensors as host arrays (views of p and g), in the reference's optimizer order."""
+    off = segs.offsets
+    ts = (Tensor * len(segs))()
+    for i in range(len(segs)):
+        ts[i].w = p[off[i]:].ctypes.data
+        ts[i].dw = g[off[i]:].ctypes.data
+        ts[i].n = segs.sizes[i]
+        ts[i].flags = segs.flags[i]
+    opt = L.anni_lm_adam_create(ts, len(segs), DT_F32, DT_F32)
+    assert opt and opt.contents.n == segs.n
+    o = opt.contents
+    assert (o.t, o.beta1, o.beta2, o.eps, o.weight_decay, o.grad_clip) == (0, 0.9, 0.999, 1e-8, 0.0, 0.0)
+    return opt
+
+
+def test_optimizer_object_trajectory_with_schedule_and_static_loss_scale(oracle, tmp_path):
+    """Config-2 style: gradients pre-multiplied by a static loss scale of 1024, LR from the
+    warm-up/cosine schedule evaluated at opt->t before the step, twelve consecutive steps; a
+    checkpoint written after step 6 and resumed into a fresh object gives the same final state."""
+    L = _mirror()
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    p0, _, _, _ = make_inputs(n, seed=51)
+    rng = np.random.default_rng(52)
+    grads = [(rng.normal(0, 1e-3, n) * 1024).astype(np.float32) for _ in range(12)]
+
+    def run(opt, p, g, first, last):
+        o = opt.contents
+        o.beta2, o.weight_decay, o.grad_clip = 0.95, 0.1, 1.0
+        for s in range(first, last):
+            g[:] = grads[s]
+            lr = schedule.lr_at(3e-4, o.t, 100, 1000, "cosine")
+            assert L.anni_lm_adam_step_scaled(opt, lr, 1.0 / 1024) == 0
+            assert o.t == s + 1 and o.last_skipped == 0
+            assert not g.any()                                    # host gradients zeroed by the step
+
+    p, g = p0.copy(), np.zeros(n, np.float32)
+    opt = _make_opt(L, segs, p, g)
+    run(opt, p, g, 0, 6)
+    assert L.anni_lm_adam_sync_host(opt) == 0
+    o = opt.contents
+    m6 = np.ctypeslib.as_array(o.h_m, (n,)).copy()
+    v6 = np.ctypeslib.as_array(o.h_v, (n,)).copy()
+    ck = str(tmp_path / "mid.adam")
+    checkpoint.write_adam(ck, m6, v6, t=o.t, epoch=0, step=6)
+    p6 = p.copy()
+    run(opt, p, g, 6, 12)
+    assert L.anni_lm_adam_sync_host(opt) == 0
+    mA = np.ctypeslib.as_array(o.h_m, (n,)).copy()
+    pA = p.copy()
+    norm_last = o.last_grad_norm
+    L.anni_lm_adam_free(C.byref(opt))
+
+    # oracle trajectory
+    rp, rm, rv = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for s in range(12):
+        gg = grads[s].copy()
+        info = oracle.step(rp, gg, rm, rv, lr=oracle.lr_schedule(3e-4, s, 100, 1000), beta1=0.9, beta2=0.95,
+                           eps=1e-8, wd=0.1, clip=1.0, grad_scale=1.0 / 1024, t_before=s, check_finite=True,
+                           seg_off=segs.offsets, seg_flags=segs.flag_array)
+    assert abs(norm_last - info["norm"]) <= 1e-9 * info["norm"]
+    # twelve steps of <= 1 ulp each may drift a little; stay within a few ulp of the oracle
+    assert f32_ulp_dist(mA, rm).max() <= 4
+    dp = np.abs(pA.astype(np.float64) - rp)
+    assert (dp <= 4 * np.spacing(np.abs(rp)) + 12e-6 * 3e-4).all()
+
+    # resume from the checkpoint in a fresh object
+    back = checkpoint.read_adam(ck, n)
+    p2, g2 = p6.copy(), np.zeros(n, np.float32)
+    opt2 = _make_opt(L, segs, p2, g2)
+    assert L.anni_lm_adam_set_moments(opt2, back["m"].ctypes.data, back["v"].ctypes.data) == 0
+    opt2.contents.t = back["t"]
+    run(opt2, p2, g2, 6, 12)
+    assert L.anni_lm_adam_sync_host(opt2) == 0
+    assert np.array_equal(p2, pA)                                 # bit-identical to the uninterrupted run
+    assert np.array_equal(np.ctypeslib.as_array(opt2.contents.h_m, (n,)), mA)
+    L.anni_lm_adam_free(C.byref(opt2))
+
+
+def test_optimizer_object_semantics(oracle):
+    """lr <= 0 is a no-op; t advances on a skipped step; invalidate re-reads host weights;
+    offload keeps m/v on the host between steps; free writes the weights back."""
+    L = _mirror()
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="all")
+    n = segs.n
+    p, g0, _, _ = make_inputs(n, seed=61)
+    g = g0.copy()
+    opt = _make_opt(L, segs, p, g)
+    o = opt.contents
+    o.grad_clip = 1.0
+    assert L.anni_lm_adam_step(opt, 0.0) == 0 and o.t == 0 and np.array_equal(g, g0)
+    p_before = p.copy()
+    g[n // 2] = np.nan
+    assert L.anni_lm_adam_step(opt, 1e-3) == 0
+    assert o.t == 1 and o.last_skipped == 1 and not np.isfinite(o.last_grad_norm)
+    assert L.anni_lm_adam_sync_host(opt) == 0 and np.array_equal(p, p_before) and not g.any()
+    # host rewrites the weights -> invalidate -> the next step starts from the new values
+    p[:] = p_before * 2
+    L.anni_lm_adam_invalidate(opt)
+    L.anni_lm_adam_set_offload(1)
+    g[:] = g0
+    assert L.anni_lm_adam_step(opt, 1e-3) == 0 and o.t == 2 and o.last_skipped == 0
+    assert not o.d_m and not o.d_v and o.dev_mv == 0              # offloaded after the step
+    rp, rm, rv, rg = p_before * 2, np.zeros(n, np.float32), np.zeros(n, np.float32), g0.copy()
+    oracle.step(rp, rg, rm, rv, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, clip=1.0, t_before=1,
+                check_finite=True)
+    hm = np.ctypeslib.as_array(o.h_m, (n,))
+    assert f32_ulp_dist(hm, rm).max() <= 1
+    g[:] = g0
+    assert L.anni_lm_adam_step(opt, 1e-3) == 0 and o.t == 3        # m/v re-uploaded from the host copy
+    rg = g0.copy()
+    oracle.step(rp, rg, rm, rv, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, clip=1.0, t_before=2,
+                check_finite=True)
+    L.anni_lm_adam_set_offload(0)
+    L.anni_lm_adam_free(C.byref(opt))                              # pulls the weights back first
+    assert (np.abs(p.astype(np.float64) - rp) <= 2 * np.spacing(np.abs(rp)) + 2e-9).all()
