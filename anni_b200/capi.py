@@ -12,7 +12,7 @@ _LIB = None
 
 DT_F32, DT_BF16 = 0, 1
 SEG_WD, SEG_TWIN_BF16, SEG_TWIN_FP8 = 1, 2, 4
-STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE = 1, 2, 4
+STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE, STEP_EXACT_UPDATE = 1, 2, 4, 8
 OK, E_ARG, E_CUDA, E_BARRIER_TIMEOUT, E_NOMEM, E_LIMIT = 0, -1, -2, -3, -4, -5
 NOALLOC_MAX_SEG = 1024
 
@@ -48,7 +48,9 @@ def lib():
     path = _build.LIB
     if not os.path.exists(path) or (_build.needs_build() and _build.shutil.which("nvcc")):
         path = _build.build()
-    L = C.CDLL(path, mode=C.RTLD_GLOBAL)
+    # RTLD_LOCAL on purpose: the library defines the reference's gpu_* symbol set, which must not
+    # interpose the same names inside other libraries of the process (e.g. the CPU checker).
+    L = C.CDLL(path, mode=C.RTLD_LOCAL)
     vp, i, d = C.c_void_p, C.c_int, C.c_double
     L.anni_optstep_create.restype = i
     L.anni_optstep_create.argtypes = [C.POINTER(Config), C.POINTER(vp)]

@@ -39,6 +39,10 @@ struct f32x8 {
 	float	x[ANNI_VEC];
 };
 
+struct f32x4 {
+	float	x[ANNI_UVEC];
+};
+
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
 {
 	uint32_t v;
@@ -193,6 +197,56 @@ template <> struct io8<__nv_bfloat16> {
 	}
 };
 
+/* four consecutive elements starting at element index e: one 16-byte (fp32) or 8-byte (bf16) access */
+template <typename T> struct io4;
+
+template <> struct io4<float> {
+	static __device__ __forceinline__ f32x4 load(const void *base, uint64_t e)
+	{
+		const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const float *>(base) + e));
+		f32x4 r;
+
+		r.x[0] = __uint_as_float(a.x);
+		r.x[1] = __uint_as_float(a.y);
+		r.x[2] = __uint_as_float(a.z);
+		r.x[3] = __uint_as_float(a.w);
+		return r;
+	}
+	static __device__ __forceinline__ void store(void *base, uint64_t e, const f32x4 &r)
+	{
+		__stcs(reinterpret_cast<uint4 *>(static_cast<float *>(base) + e),
+		    make_uint4(__float_as_uint(r.x[0]), __float_as_uint(r.x[1]), __float_as_uint(r.x[2]),
+		    __float_as_uint(r.x[3])));
+	}
+	static __device__ __forceinline__ void zero(void *base, uint64_t e)
+	{
+		__stcs(reinterpret_cast<uint4 *>(static_cast<float *>(base) + e), make_uint4(0, 0, 0, 0));
+	}
+};
+
+template <> struct io4<__nv_bfloat16> {
+	static __device__ __forceinline__ f32x4 load(const void *base, uint64_t e)
+	{
+		const uint2 q = __ldcs(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(base) + e));
+		f32x4 r;
+
+		r.x[0] = __uint_as_float(q.x << 16);
+		r.x[1] = __uint_as_float(q.x & 0xffff0000u);
+		r.x[2] = __uint_as_float(q.y << 16);
+		r.x[3] = __uint_as_float(q.y & 0xffff0000u);
+		return r;
+	}
+	static __device__ __forceinline__ void store(void *base, uint64_t e, const f32x4 &r)
+	{
+		__stcs(reinterpret_cast<uint2 *>(static_cast<uint16_t *>(base) + e),
+		    make_uint2(pack_bf16x2(r.x[0], r.x[1]), pack_bf16x2(r.x[2], r.x[3])));
+	}
+	static __device__ __forceinline__ void zero(void *base, uint64_t e)
+	{
+		__stcs(reinterpret_cast<uint2 *>(static_cast<uint16_t *>(base) + e), make_uint2(0, 0));
+	}
+};
+
 /* largest s with seg_off[s] <= x (x inside [seg_off[0], seg_off[n_seg])) */
 __device__ __forceinline__ int seg_find(const int64_t *seg_off, int n_seg, int64_t x)
 {
@@ -224,12 +278,13 @@ struct chunk_walk {
 	uint32_t	sc;
 };
 
-__device__ __forceinline__ chunk_walk walk_init(uint64_t n, int sc_log2)
+/* chunk_log2: log2 of the elements per chunk (ANNI_CHUNK_LOG2 or ANNI_UCHUNK_LOG2) */
+__device__ __forceinline__ chunk_walk walk_init(uint64_t n, int sc_log2, int chunk_log2)
 {
 	chunk_walk w;
 	const uint64_t per_round = (uint64_t)gridDim.x << sc_log2;
 
-	w.chunks = (n + ANNI_CHUNK - 1) / ANNI_CHUNK;
+	w.chunks = (n + ((uint64_t)1 << chunk_log2) - 1) >> chunk_log2;
 	w.sc = (uint32_t)sc_log2;
 	w.iters = ((w.chunks + per_round - 1) / per_round) << sc_log2;
 	return w;
@@ -324,32 +379,61 @@ __device__ __forceinline__ double sum_partials(const anni_control *ctl, int npar
 /* ---- phase A: sum of squares of this block's chunks ---------------------- */
 
 template <typename GradT>
-__device__ __forceinline__ double norm_phase(const anni_launch &a, const chunk_walk &w)
+__device__ __forceinline__ void norm_accumulate(const f32x8 &g, double &acc0, double &acc1)
 {
+	/* squares and their sum in double: the skip decision and the clip factor then
+	** agree with a double accumulation to the last bits */
+#pragma unroll
+	for (int k = 0; k < ANNI_VEC; k += 2) {
+		const double g0 = (double)g.x[k];
+		const double g1 = (double)g.x[k + 1];
+
+		acc0 = fma(g0, g0, acc0);
+		acc1 = fma(g1, g1, acc1);
+	}
+}
+
+template <typename GradT>
+__device__ __forceinline__ double norm_phase(const anni_launch &a)
+{
+	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_CHUNK_LOG2);
 	double acc0 = 0.0;
 	double acc1 = 0.0;
 	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	uint64_t it = 0;
 
-#pragma unroll 2
-	for (uint64_t it = 0; it < w.iters; it++) {
+	/* four chunks per trip while whole aligned chunks last: four independent 16-byte loads in flight */
+	if (a.aligned) {
+		for (; it + 4 <= w.iters; it += 4) {
+			const uint64_t c0 = walk_chunk(w, it);
+			const uint64_t c1 = walk_chunk(w, it + 1);
+			const uint64_t c2 = walk_chunk(w, it + 2);
+			const uint64_t c3 = walk_chunk(w, it + 3);
+			const uint64_t cmax = max(max(c0, c1), max(c2, c3));
+
+			if ((cmax + 1) * ANNI_CHUNK > a.n)
+				break;
+			const f32x8 g0 = io8<GradT>::load_keep(a.grad, c0 * ANNI_CHUNK + t8);
+			const f32x8 g1 = io8<GradT>::load_keep(a.grad, c1 * ANNI_CHUNK + t8);
+			const f32x8 g2 = io8<GradT>::load_keep(a.grad, c2 * ANNI_CHUNK + t8);
+			const f32x8 g3 = io8<GradT>::load_keep(a.grad, c3 * ANNI_CHUNK + t8);
+
+			norm_accumulate<GradT>(g0, acc0, acc1);
+			norm_accumulate<GradT>(g1, acc0, acc1);
+			norm_accumulate<GradT>(g2, acc0, acc1);
+			norm_accumulate<GradT>(g3, acc0, acc1);
+		}
+	}
+	for (; it < w.iters; it++) {
 		const uint64_t c = walk_chunk(w, it);
 		const uint64_t e = c * ANNI_CHUNK + t8;
 
 		if (c >= w.chunks)
 			continue;
 		if (a.aligned && e + ANNI_VEC <= a.n) {
-			f32x8 g = io8<GradT>::load_keep(a.grad, e);
+			const f32x8 g = io8<GradT>::load_keep(a.grad, e);
 
-			/* squares and their sum in double: the skip decision and the clip
-			** factor then agree with a double accumulation to the last bits */
-#pragma unroll
-			for (int k = 0; k < ANNI_VEC; k += 2) {
-				const double g0 = (double)g.x[k];
-				const double g1 = (double)g.x[k + 1];
-
-				acc0 = fma(g0, g0, acc0);
-				acc1 = fma(g1, g1, acc1);
-			}
+			norm_accumulate<GradT>(g, acc0, acc1);
 		} else {
 			for (int k = 0; k < ANNI_VEC; k++)
 				if (e + k < a.n) {
@@ -393,6 +477,7 @@ __device__ __forceinline__ decision decide(const anni_launch &a, double ss, doub
 
 /* ---- phase B: AdamW on one element ----------------------------------------- */
 
+template <bool EXACT>
 __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, float lrwd,
 	float gf, float &p, float &m, float &v)
 {
@@ -410,6 +495,32 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	** moves p by far less than one ulp unless p itself is of the size of the
 	** update.  Every product is rounded on its own (no contraction).
 	*/
+	if (EXACT) {
+		/*
+		** The reference's double expression lr*(m/bc1)/(sqrt(v/bc2)+eps) from the
+		** rounded float moments: reciprocal square root and reciprocal start from
+		** the SFU's 64-bit seeds (about 20 bits) and take one Newton step each
+		** (relative error ~1e-12), so p - u rounds to the reference's float in
+		** all but about one element in ten million.
+		*/
+		const double vr = (double)v;
+		const double x = vr * a.ibc2d;
+		const double hx = vr * (0.5 * a.ibc2d);
+		double y;
+		double q;
+
+		asm("rsqrt.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(x));
+		y = y * fma(-hx * y, y, 1.5);
+		const double dn = (v > 0.0f ? x * y : 0.0) + a.epsd;
+
+		asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(q) : "d"(dn));
+		q = fma(fma(-dn, q, 1.0), q, q);
+		const float p1 = __double2float_rn((double)p - (a.lrbc1d * (double)m) * q);
+
+		/* decay on the stored float, in double as the reference does, rounded once */
+		p = lrwd != 0.0f ? __double2float_rn(fma(-a.lrwdd, (double)p1, (double)p1)) : p1;
+		return;
+	}
 	const float den = __fadd_rn(sqrt_approx(__fmul_rn(v, a.ibc2)), a.eps);
 	const float upd = __fmul_rn(__fmul_rn(a.lrbc1, m), rcp_approx(den));
 
@@ -417,39 +528,39 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	p = __fmaf_rn(-lrwd, p, p);
 }
 
-template <typename GradT, typename StateT>
+template <typename GradT, typename StateT, bool EXACT>
 __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t e, double coef,
 	uint32_t sflags, float &tmax)
 {
 	const float lrwd = (sflags & ANNI_SEG_WD) ? a.lrwd : 0.0f;
-	f32x8 g = io8<GradT>::load(a.grad, e);
-	f32x8 p = io8<float>::load(a.master, e);
-	f32x8 m = io8<StateT>::load(a.m, e);
-	f32x8 v = io8<StateT>::load(a.v, e);
+	f32x4 g = io4<GradT>::load(a.grad, e);
+	f32x4 p = io4<float>::load(a.master, e);
+	f32x4 m = io4<StateT>::load(a.m, e);
+	f32x4 v = io4<StateT>::load(a.v, e);
 
 #pragma unroll
-	for (int k = 0; k < ANNI_VEC; k++)
-		adam_elem(a, coef, lrwd, g.x[k], p.x[k], m.x[k], v.x[k]);
-	io8<float>::store(a.master, e, p);
-	io8<StateT>::store(a.m, e, m);
-	io8<StateT>::store(a.v, e, v);
+	for (int k = 0; k < ANNI_UVEC; k++)
+		adam_elem<EXACT>(a, coef, lrwd, g.x[k], p.x[k], m.x[k], v.x[k]);
+	io4<float>::store(a.master, e, p);
+	io4<StateT>::store(a.m, e, m);
+	io4<StateT>::store(a.v, e, v);
 	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16)
-		io8<__nv_bfloat16>::store(a.twin16, e, p);
+		io4<__nv_bfloat16>::store(a.twin16, e, p);
 	if (sflags & ANNI_SEG_TWIN_FP8) {
 #pragma unroll
-		for (int k = 0; k < ANNI_VEC; k++)
+		for (int k = 0; k < ANNI_UVEC; k++)
 			tmax = fmaxf(tmax, fabsf(p.x[k]));
 	}
 	if (a.flags & ANNI_STEP_ZERO_GRAD)
-		io8<GradT>::zero(a.grad, e);
+		io4<GradT>::zero(a.grad, e);
 }
 
 /* element-wise path for chunks that cross a tensor boundary, the arena end, or unaligned buffers */
-template <typename GradT, typename StateT>
+template <typename GradT, typename StateT, bool EXACT>
 __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64_t e, double coef,
 	bool skip)
 {
-	for (int k = 0; k < ANNI_VEC; k++) {
+	for (int k = 0; k < ANNI_UVEC; k++) {
 		const uint64_t i = e + k;
 
 		if (i >= a.n)
@@ -462,7 +573,7 @@ __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64
 			float m = io8<StateT>::load1(a.m, i);
 			float v = io8<StateT>::load1(a.v, i);
 
-			adam_elem(a, coef, lrwd, io8<GradT>::load1(a.grad, i), p, m, v);
+			adam_elem<EXACT>(a, coef, lrwd, io8<GradT>::load1(a.grad, i), p, m, v);
 			a.master[i] = p;
 			io8<StateT>::store1(a.m, i, m);
 			io8<StateT>::store1(a.v, i, v);
@@ -489,11 +600,11 @@ __device__ __forceinline__ void amax_flush(const anni_launch &a, int seg, float 
 	tmax = 0.0f;
 }
 
-template <typename GradT, typename StateT>
-__device__ __forceinline__ void update_phase(const anni_launch &a, const chunk_walk &w,
-	const decision &d)
+template <typename GradT, typename StateT, bool EXACT>
+__device__ __forceinline__ void update_phase(const anni_launch &a, const decision &d)
 {
-	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_UCHUNK_LOG2);
+	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
 	float tmax = 0.0f;
 	int seg = -1;
 	int amax_seg = -1;
@@ -503,7 +614,7 @@ __device__ __forceinline__ void update_phase(const anni_launch &a, const chunk_w
 	/* backwards: the chunks read last by the norm phase are the likeliest to sit in L2 */
 	for (uint64_t it = w.iters; it > 0; it--) {
 		const uint64_t c = walk_chunk(w, it - 1);
-		const uint64_t base = c * ANNI_CHUNK;
+		const uint64_t base = c * ANNI_UCHUNK;
 		const int64_t abase = (int64_t)(a.arena_off + base);
 		bool whole;
 
@@ -513,8 +624,8 @@ __device__ __forceinline__ void update_phase(const anni_launch &a, const chunk_w
 			seg = seg_find(a.seg_off, a.n_seg, abase);
 		while (abase < a.seg_off[seg])
 			seg--;
-		whole = a.aligned && base + ANNI_CHUNK <= a.n
-		    && abase + ANNI_CHUNK <= a.seg_off[seg + 1];
+		whole = a.aligned && base + ANNI_UCHUNK <= a.n
+		    && abase + ANNI_UCHUNK <= a.seg_off[seg + 1];
 		if (whole && !d.skip) {
 			const uint32_t sflags = a.seg_flags[seg];
 
@@ -523,11 +634,11 @@ __device__ __forceinline__ void update_phase(const anni_launch &a, const chunk_w
 					amax_flush(a, amax_seg, tmax);
 				amax_seg = (sflags & ANNI_SEG_TWIN_FP8) ? seg : -1;
 			}
-			update_chunk_vec<GradT, StateT>(a, base + t8, d.coef, sflags, tmax);
+			update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax);
 		} else if (whole) {
-			io8<GradT>::zero(a.grad, base + t8);	/* skipped step: only the gradients change */
+			io4<GradT>::zero(a.grad, base + t4);	/* skipped step: only the gradients change */
 		} else
-			update_chunk_scalar<GradT, StateT>(a, base + t8, d.coef, d.skip);
+			update_chunk_scalar<GradT, StateT, EXACT>(a, base + t4, d.coef, d.skip);
 	}
 	if (amax_seg >= 0)
 		amax_flush(a, amax_seg, tmax);
@@ -546,9 +657,10 @@ __device__ __forceinline__ float fp8_scale(float amax)
 	return s < 1e-12f ? 1e-12f : s;
 }
 
-__device__ __forceinline__ void quantize_phase(const anni_launch &a, const chunk_walk &w)
+__device__ __forceinline__ void quantize_phase(const anni_launch &a)
 {
-	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_UCHUNK_LOG2);
+	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
 	int seg = -1;
 
 	if (!a.twin8)
@@ -559,7 +671,7 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a, const chunk
 				a.seg_scale[s] = fp8_scale(a.seg_amax[s]);
 	for (uint64_t it = 0; it < w.iters; it++) {
 		const uint64_t c = walk_chunk(w, it);
-		const uint64_t base = c * ANNI_CHUNK;
+		const uint64_t base = c * ANNI_UCHUNK;
 		const int64_t abase = (int64_t)(a.arena_off + base);
 
 		if (c >= w.chunks)
@@ -568,26 +680,21 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a, const chunk
 			seg = seg_find(a.seg_off, a.n_seg, abase);
 		while (abase >= a.seg_off[seg + 1])
 			seg++;
-		if (a.aligned && base + ANNI_CHUNK <= a.n && abase + ANNI_CHUNK <= a.seg_off[seg + 1]) {
+		if (a.aligned && base + ANNI_UCHUNK <= a.n && abase + ANNI_UCHUNK <= a.seg_off[seg + 1]) {
 			if (a.seg_flags[seg] & ANNI_SEG_TWIN_FP8) {
 				const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[seg]));
-				const uint64_t e = base + t8;
-				f32x8 p = io8<float>::load(a.master, e);
-				uint2 q;
+				const uint64_t e = base + t4;
+				f32x4 p = io4<float>::load(a.master, e);
+				const uint32_t q = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[0] * inv,
+				    p.x[1] * inv), __NV_SATFINITE, __NV_E4M3)
+				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[2] * inv, p.x[3] * inv),
+				    __NV_SATFINITE, __NV_E4M3) << 16);
 
-				q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[0] * inv, p.x[1] * inv),
-				    __NV_SATFINITE, __NV_E4M3)
-				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[2] * inv,
-				    p.x[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
-				q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[4] * inv, p.x[5] * inv),
-				    __NV_SATFINITE, __NV_E4M3)
-				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[6] * inv,
-				    p.x[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
-				__stcs(reinterpret_cast<uint2 *>(a.twin8 + e), q);
+				__stcs(reinterpret_cast<uint32_t *>(a.twin8 + e), q);
 			}
 		} else {
-			for (int k = 0; k < ANNI_VEC; k++) {
-				const uint64_t i = base + t8 + k;
+			for (int k = 0; k < ANNI_UVEC; k++) {
+				const uint64_t i = base + t4 + k;
 
 				if (i >= a.n)
 					break;
@@ -641,10 +748,9 @@ template <typename GradT>
 __global__ void __launch_bounds__(ANNI_THREADS, 4) norm_kernel(const anni_launch a)
 {
 	__shared__ int s_last;
-	const chunk_walk w = walk_init(a.n, a.sc_log2);
 	double s;
 
-	s = block_sum(norm_phase<GradT>(a, w));
+	s = block_sum(norm_phase<GradT>(a));
 	if (threadIdx.x == 0) {
 		a.ctl->partials[blockIdx.x] = s;
 		__threadfence();
@@ -666,10 +772,9 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) norm_kernel(const anni_launch
 }
 
 /* Update only (second launch of the split sequence, or the legacy call with a host multiplier). */
-template <typename GradT, typename StateT>
+template <typename GradT, typename StateT, bool EXACT>
 __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_launch a)
 {
-	const chunk_walk w = walk_init(a.n, a.sc_log2);
 	decision d;
 
 	if (a.flags & ANNI_LAUNCH_HOST_COEF) {
@@ -684,22 +789,21 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_laun
 			a.ctl->skipped = d.skip ? 1 : 0;
 		}
 	}
-	update_phase<GradT, StateT>(a, w, d);
+	update_phase<GradT, StateT, EXACT>(a, d);
 	step_epilogue(a.ctl, d.skip);
 }
 
 /* The whole step in one cooperative launch. */
-template <typename GradT, typename StateT>
+template <typename GradT, typename StateT, bool EXACT>
 __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launch a)
 {
-	const chunk_walk w = walk_init(a.n, a.sc_log2);
 	decision d;
 	double ss = 0.0;
 	uint32_t barriers = 0;
 	const double loss_scale = a.ctl->loss_scale;
 
 	if (a.flags & ANNI_LAUNCH_NEED_NORM) {
-		double s = block_sum(norm_phase<GradT>(a, w));
+		double s = block_sum(norm_phase<GradT>(a));
 
 		if (threadIdx.x == 0)
 			a.ctl->partials[blockIdx.x] = s;
@@ -715,11 +819,11 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launc
 		a.ctl->eff_scale = d.coef;
 		a.ctl->skipped = d.skip ? 1 : 0;
 	}
-	update_phase<GradT, StateT>(a, w, d);
+	update_phase<GradT, StateT, EXACT>(a, d);
 	if ((a.flags & ANNI_LAUNCH_HAS_FP8) && !d.skip) {
 		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
 			return;
-		quantize_phase(a, w);
+		quantize_phase(a);
 	}
 	step_epilogue(a.ctl, d.skip);
 }
@@ -729,7 +833,7 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) quantize_kernel(const anni_la
 {
 	if (a.ctl->skipped)
 		return;
-	quantize_phase(a, walk_init(a.n, a.sc_log2));
+	quantize_phase(a);
 }
 
 /* One-shot fp32 -> bf16 of a flat buffer (seeding the twin; num/gpu.h:73 of the reference). */
@@ -779,7 +883,10 @@ template <typename K> int occupancy_blocks(K kernel)
 template <typename GradT, typename StateT>
 int launch_update_t(const anni_launch *a, int blocks, cudaStream_t st)
 {
-	update_kernel<GradT, StateT><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	if (a->flags & ANNI_STEP_EXACT_UPDATE)
+		update_kernel<GradT, StateT, true><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	else
+		update_kernel<GradT, StateT, false><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
 
@@ -787,9 +894,23 @@ template <typename GradT, typename StateT>
 int launch_fused_t(const anni_launch *a, int blocks, cudaStream_t st)
 {
 	void *args[] = { (void *)a };
+	const void *k = (a->flags & ANNI_STEP_EXACT_UPDATE)
+	    ? (const void *)fused_kernel<GradT, StateT, true>
+	    : (const void *)fused_kernel<GradT, StateT, false>;
 
-	return cudaLaunchCooperativeKernel((const void *)fused_kernel<GradT, StateT>, dim3(blocks),
-	    dim3(ANNI_THREADS), args, 0, st) == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+	return cudaLaunchCooperativeKernel(k, dim3(blocks), dim3(ANNI_THREADS), args, 0, st)
+	    == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+/* resident blocks of the heavier (exact) variant: both variants then run with the same grid */
+template <typename GradT, typename StateT> int grid_t(int cooperative)
+{
+	const int a = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true>)
+	    : occupancy_blocks(update_kernel<GradT, StateT, true>);
+	const int b = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false>)
+	    : occupancy_blocks(update_kernel<GradT, StateT, false>);
+
+	return a < b ? a : b;
 }
 
 }	/* namespace */
@@ -809,22 +930,13 @@ extern "C" int anni_grid_blocks(int grad_dtype, int state_dtype, int cooperative
 	const bool gb = grad_dtype == ANNI_DT_BF16;
 	const bool sb = state_dtype == ANNI_DT_BF16;
 
-	if (cooperative) {
-		if (gb && sb)
-			return occupancy_blocks(fused_kernel<__nv_bfloat16, __nv_bfloat16>);
-		if (gb)
-			return occupancy_blocks(fused_kernel<__nv_bfloat16, float>);
-		if (sb)
-			return occupancy_blocks(fused_kernel<float, __nv_bfloat16>);
-		return occupancy_blocks(fused_kernel<float, float>);
-	}
 	if (gb && sb)
-		return occupancy_blocks(update_kernel<__nv_bfloat16, __nv_bfloat16>);
+		return grid_t<__nv_bfloat16, __nv_bfloat16>(cooperative);
 	if (gb)
-		return occupancy_blocks(update_kernel<__nv_bfloat16, float>);
+		return grid_t<__nv_bfloat16, float>(cooperative);
 	if (sb)
-		return occupancy_blocks(update_kernel<float, __nv_bfloat16>);
-	return occupancy_blocks(update_kernel<float, float>);
+		return grid_t<float, __nv_bfloat16>(cooperative);
+	return grid_t<float, float>(cooperative);
 }
 
 /*
@@ -851,6 +963,10 @@ extern "C" int anni_fill_hyper(anni_launch *a, const anni_optstep_hyper *hp)
 	a->b2 = hp->beta2;
 	a->omb2 = 1.0 - hp->beta2;
 	a->lrbc1 = (float)(hp->lr / bc1);
+	a->lrbc1d = hp->lr / bc1;
+	a->lrwdd = hp->weight_decay > 0.0 ? hp->lr * hp->weight_decay : 0.0;
+	a->ibc2d = 1.0 / bc2;
+	a->epsd = hp->eps;
 	a->ibc2 = (float)(1.0 / bc2);
 	a->eps = (float)hp->eps;
 	a->lrwd = hp->weight_decay > 0.0 ? (float)(hp->lr * hp->weight_decay) : 0.0f;

@@ -122,6 +122,15 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 		h->blocks_split = h->blocks_coop;
 	else
 		h->blocks_coop = h->blocks_split;
+	{
+		/* ANNI_B200_BLOCKS_PER_SM=k: fewer resident blocks than fit (tuning knob) */
+		const char *e = getenv("ANNI_B200_BLOCKS_PER_SM");
+		int sms = 0;
+
+		if (e && atoi(e) > 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount,
+		    h->device) == cudaSuccess && sms > 0 && atoi(e) * sms < h->blocks_coop)
+			h->blocks_coop = h->blocks_split = atoi(e) * sms;
+	}
 	h->la.n = cfg->shard_n;
 	h->la.arena_off = cfg->shard_off;
 	h->la.seg_off = h->d_seg_off;

@@ -10,8 +10,19 @@
 #include "anni_b200.h"
 
 #define ANNI_THREADS		256	/* threads per block of every arena kernel */
-#define ANNI_VEC		8	/* elements per thread per chunk */
+#define ANNI_VEC		8	/* elements per thread per chunk, norm phase (16-byte loads of bf16) */
 #define ANNI_CHUNK		(ANNI_THREADS * ANNI_VEC)
+#define ANNI_CHUNK_LOG2		11
+/*
+** Update and quantise phases: four elements per thread per chunk.  Measured on
+** B200 with the update's access mix (5 read and 6 write streams): HBM
+** throughput peaks when about 4096 elements per SM are in flight and drops
+** ~7 % at twice that, while the arithmetic wants 1024 threads per SM to hide
+** its latencies -- hence 4 blocks x 256 threads x 4 elements.
+*/
+#define ANNI_UVEC		4
+#define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
+#define ANNI_UCHUNK_LOG2	10
 #define ANNI_MAX_BLOCKS		2048	/* capacity of the per-block partial table */
 /* polls of a bounded device wait before it gives up (each poll sleeps >= 32 ns) */
 #define ANNI_WAIT_POLLS		(1u << 23)
@@ -64,6 +75,10 @@ typedef struct anni_launch {
 	double		omb1;
 	double		b2;
 	double		omb2;
+	double		lrbc1d;		/* the same three in double */
+	double		ibc2d;
+	double		epsd;
+	double		lrwdd;		/* lr * weight_decay */
 	float		lrbc1;		/* lr / (1 - beta1^t) */
 	float		ibc2;		/* 1 / (1 - beta2^t) */
 	float		eps;

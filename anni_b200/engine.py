@@ -203,12 +203,13 @@ class OptStep:
     # -- stepping ---------------------------------------------------------------------
     @staticmethod
     def hyper(*, lr, t, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, clip=0.0, grad_scale=1.0,
-              check_finite=True, zero_grad=True, dev_loss_scale=False):
+              check_finite=True, zero_grad=True, dev_loss_scale=False, exact=False):
         hp = capi.Hyper()
         hp.lr, hp.beta1, hp.beta2, hp.eps = lr, beta1, beta2, eps
         hp.weight_decay, hp.grad_clip, hp.grad_scale, hp.t = wd, clip, grad_scale, int(t)
         hp.flags = ((STEP_CHECK_FINITE if check_finite else 0) | (STEP_ZERO_GRAD if zero_grad else 0)
-                    | (STEP_DEV_LOSS_SCALE if dev_loss_scale else 0))
+                    | (STEP_DEV_LOSS_SCALE if dev_loss_scale else 0)
+                    | (capi.STEP_EXACT_UPDATE if exact else 0))
         return hp
 
     def _stream(self, stream):

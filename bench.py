@@ -219,10 +219,10 @@ def run_ours(args):
             z.grad_shard = buf[:z.per]
             z.eng.bind(z.master, z.m, z.v, z.grad_shard, z.twin_shard, z.twin8_shard)
 
-    def hyper(t):
+    def hyper(t, exact=False):
         return OptStep.hyper(lr=HYPER["lr"], t=t, beta1=HYPER["beta1"], beta2=HYPER["beta2"],
                              eps=HYPER["eps"], wd=HYPER["wd"], clip=HYPER["clip"],
-                             grad_scale=1.0 / world, check_finite=True, zero_grad=True)
+                             grad_scale=1.0 / world, check_finite=True, zero_grad=True, exact=exact)
 
     def barrier():
         if world > 1:
@@ -288,6 +288,27 @@ def run_ours(args):
     ms_per_step = total_ms / K
     value = n / (ms_per_step * 1e-3)
 
+    # ---- the same step with the parameter update evaluated in double (ANNI_STEP_EXACT_UPDATE) ----
+    exact_ms = None
+    if world == 1:
+        refill()
+        k_ex = min(10, pool_n - 2)
+        for i in range(2):
+            bind_grads(pool[i])
+            z.step(hyper(t, exact=True))
+            t += 1
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(k_ex):
+            bind_grads(pool[2 + i])
+            z.step(hyper(t, exact=True))
+            t += 1
+        e1.record()
+        barrier()
+        exact_ms = e0.elapsed_time(e1) / k_ex
+
     # ---- e2e: host gradient buffers through the C ABI --------------------------------------
     e2e_steps = max(2, min(5, K))
     host = [torch.empty(z.padded, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
@@ -333,6 +354,7 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "n_params": n, "grads": "bf16", "master": "fp32",
                    "moments": "bf16", "twins": "bf16", "clip": HYPER["clip"], "wd": "0.1 on matrices",
+                   "update_arithmetic": "double moments, float update (fast mode)",
                    "zero_grad": True, "zero1_ranks": world,
                    "l2": "inputs larger than L2 (6.7 GB state + a fresh 1.1 GB gradient arena per step)",
                    "hbm_gbs_alg": (ALG_BYTES_PER_PARAM * n / (ms_per_step * 1e-3) / 1e9)},
@@ -352,6 +374,9 @@ def run_ours(args):
     if world > 1:
         line["phases_ms"] = {k: v / K for k, v in phase_ms.items()}
     if world == 1:
+        line["exact_update"] = {"ms_per_step": exact_ms, "value": n / (exact_ms * 1e-3),
+                                "roofline_frac": ALG_BYTES_PER_PARAM * n / (exact_ms * 1e-3) / 1e9 / peak,
+                                "note": "same step with ANNI_STEP_EXACT_UPDATE (update term in double)"}
         base, _ = cpu_reference_step_rate(64 * 1024 * 1024, 3, 1)
         line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)

@@ -117,3 +117,28 @@ def test_fp8_twins_per_tensor_scale(oracle, split):
             assert np.array_equal(out["twin"][sl], bf16_bits_from_f32(out["p"][sl])), name
             assert not out["twin8"][sl].any()
     assert n_fp8 == 12
+
+
+@pytest.mark.parametrize("grad_dtype,state_dtype", [(DT_F32, DT_F32), (DT_BF16, DT_F32), (DT_BF16, DT_BF16)])
+@pytest.mark.parametrize("t", [1, 1000])
+def test_exact_update_mode_is_bit_faithful(oracle, grad_dtype, state_dtype, t):
+    """ANNI_STEP_EXACT_UPDATE: the master equals the oracle's float bit for bit except for a
+    vanishing fraction one ulp off -- also where the parameter is as small as its update
+    (the cancellation case the fast float path cannot resolve) and at step 1, where
+    |update| = lr.  Flat bar here: at most 1 ulp anywhere, at least 99.999 % identical."""
+    from parity_util import f32_ulp_dist
+    n = 1 << 20
+    p, g, m, v = make_inputs(n, seed=70 + t, grad_dtype=grad_dtype, state_dtype=state_dtype)
+    if t == 1:
+        m[:] = 0
+        v[:] = 0
+    p[::3] *= np.float32(1e-2)                     # a third of the weights of the size of the update
+    p[1::97] = 0.0
+    kw = dict(HYP, wd=0.1, clip=0.0, grad_scale=1.0, t_before=t - 1)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, None, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(None, p, g, m, v, dict(HYP, wd=0.1, clip=0.0, grad_scale=1.0, t=t, exact=True), n_arena=n)
+    assert np.array_equal(out["m"], rm) and np.array_equal(out["v"], rv)
+    d = f32_ulp_dist(out["p"], rp)
+    assert d.max() <= 1, int(d.max())
+    assert (d == 0).mean() >= 0.99999, float((d == 0).mean())
+    assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"]))
