@@ -544,8 +544,14 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 	io4<float>::store(a.master, e, p);
 	io4<StateT>::store(a.m, e, m);
 	io4<StateT>::store(a.v, e, v);
-	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16)
-		io4<__nv_bfloat16>::store(a.twin16, e, p);
+	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16) {
+		if (a.n_peers > 0) {
+			/* the all-gather, fused: this shard's twins straight into every rank's arena */
+			for (int k = 0; k < a.n_peers; k++)
+				io4<__nv_bfloat16>::store(a.twin_peer[k], e, p);
+		} else
+			io4<__nv_bfloat16>::store(a.twin16, e, p);
+	}
 	if (sflags & ANNI_SEG_TWIN_FP8) {
 #pragma unroll
 		for (int k = 0; k < ANNI_UVEC; k++)
@@ -577,8 +583,13 @@ __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64
 			a.master[i] = p;
 			io8<StateT>::store1(a.m, i, m);
 			io8<StateT>::store1(a.v, i, v);
-			if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16)
-				io8<__nv_bfloat16>::store1(a.twin16, i, p);
+			if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16) {
+				if (a.n_peers > 0) {
+					for (int q = 0; q < a.n_peers; q++)
+						io8<__nv_bfloat16>::store1(a.twin_peer[q], i, p);
+				} else
+					io8<__nv_bfloat16>::store1(a.twin16, i, p);
+			}
 			if (sflags & ANNI_SEG_TWIN_FP8)
 				atomicMax(reinterpret_cast<int *>(&a.seg_amax[s]),
 				    __float_as_int(fabsf(p)));
@@ -690,7 +701,11 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a)
 				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[2] * inv, p.x[3] * inv),
 				    __NV_SATFINITE, __NV_E4M3) << 16);
 
-				__stcs(reinterpret_cast<uint32_t *>(a.twin8 + e), q);
+				if (a.n_peers > 0) {
+					for (int k = 0; k < a.n_peers; k++)
+						__stcs(reinterpret_cast<uint32_t *>(a.twin8_peer[k] + e), q);
+				} else
+					__stcs(reinterpret_cast<uint32_t *>(a.twin8 + e), q);
 			}
 		} else {
 			for (int k = 0; k < ANNI_UVEC; k++) {
@@ -703,8 +718,14 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a)
 				if (a.seg_flags[s] & ANNI_SEG_TWIN_FP8) {
 					const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[s]));
 
-					a.twin8[i] = (uint8_t)__nv_cvt_float_to_fp8(a.master[i] * inv,
+					const uint8_t q8 = (uint8_t)__nv_cvt_float_to_fp8(a.master[i] * inv,
 					    __NV_SATFINITE, __NV_E4M3);
+
+					if (a.n_peers > 0) {
+						for (int q = 0; q < a.n_peers; q++)
+							a.twin8_peer[q][i] = q8;
+					} else
+						a.twin8[i] = q8;
 				}
 			}
 		}
@@ -759,6 +780,173 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) norm_kernel(const anni_launch
 	__syncthreads();
 	if (s_last) {
 		/* last block: every partial is visible; same fixed order as the fused kernel */
+		double t;
+
+		__threadfence();
+		t = sum_partials(a.ctl, (int)gridDim.x);
+		if (threadIdx.x == 0) {
+			a.ctl->reduce[0] = t;
+			a.ctl->reduce[1] = isfinite(t) ? 0.0 : 1.0;
+			a.ctl->norm_ticket = 0;
+		}
+	}
+}
+
+/*
+** ZeRO-1, first half of the step in ONE kernel: the reduce-scatter and the
+** norm.  Every rank holds a full gradient arena in peer-accessible memory; this
+** rank reads its own shard out of all of them (plain 128-bit loads over NVLink /
+** NVSwitch, one per peer in flight per thread), adds them in float in rank
+** order, rounds once to the gradient type, writes the reduced shard to local
+** memory for the update phase and accumulates the sum of squares of exactly the
+** values it wrote.  Result: {sumsq, nonfinite} in the control block, as
+** norm_kernel leaves it.  The caller orders this kernel after every rank's
+** gradients are complete (a stream-ordered barrier), and all-reduces the two
+** doubles afterwards, which also tells every rank that its arena has been read.
+*/
+/* eight consecutive elements as loaded, not yet widened: keeps many peer loads in flight in few registers */
+template <typename T> struct raw8;
+
+template <> struct raw8<__nv_bfloat16> {
+	uint4	q;
+	__device__ __forceinline__ void load(const void *base, uint64_t e)
+	{
+		q = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + e));
+	}
+	__device__ __forceinline__ f32x8 widen() const
+	{
+		return unpack_bf16x8(q);
+	}
+};
+
+template <> struct raw8<float> {
+	uint4	q[2];
+	__device__ __forceinline__ void load(const void *base, uint64_t e)
+	{
+		const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const float *>(base) + e);
+
+		q[0] = __ldcs(p);
+		q[1] = __ldcs(p + 1);
+	}
+	__device__ __forceinline__ f32x8 widen() const
+	{
+		f32x8 r;
+
+		r.x[0] = __uint_as_float(q[0].x);
+		r.x[1] = __uint_as_float(q[0].y);
+		r.x[2] = __uint_as_float(q[0].z);
+		r.x[3] = __uint_as_float(q[0].w);
+		r.x[4] = __uint_as_float(q[1].x);
+		r.x[5] = __uint_as_float(q[1].y);
+		r.x[6] = __uint_as_float(q[1].z);
+		r.x[7] = __uint_as_float(q[1].w);
+		return r;
+	}
+};
+
+/* sum of one chunk's eight elements over the peers in rank order, rounded to the gradient type, stored, squared */
+template <typename GradT, int SLOTS>
+__device__ __forceinline__ void reduce_store(const anni_launch &a, const raw8<GradT> (&r)[SLOTS], int first,
+	uint64_t e, double &acc0, double &acc1)
+{
+	f32x8 sum = r[first].widen();
+
+#pragma unroll
+	for (int k = 1; k < SLOTS; k++)
+		if (k < a.n_peers) {
+			const f32x8 x = r[first + k < SLOTS ? first + k : 0].widen();
+
+#pragma unroll
+			for (int j = 0; j < ANNI_VEC; j++)
+				sum.x[j] = __fadd_rn(sum.x[j], x.x[j]);
+		}
+	if (sizeof(GradT) == 2)		/* what the update will read back: the rounded value */
+		sum = unpack_bf16x8(pack_bf16x8(sum));
+	io8<GradT>::store(a.grad, e, sum);
+	norm_accumulate<GradT>(sum, acc0, acc1);
+}
+
+/*
+** ZeRO-1, first half of the step in ONE kernel: the reduce-scatter and the
+** norm.  Every rank holds a full gradient arena in peer-accessible memory; this
+** rank reads its own shard out of all of them (plain 128-bit loads over NVLink /
+** NVSwitch), adds them in float in rank order, rounds once to the gradient type,
+** writes the reduced shard to local memory for the update phase and accumulates
+** the sum of squares of exactly the values it wrote.  Result: {sumsq,
+** nonfinite} in the control block, as norm_kernel leaves it.  A remote load
+** takes a few microseconds, so each thread keeps SLOTS of them in flight
+** (peers x consecutive chunks) before it touches the first.  The caller orders
+** this kernel after every rank's gradients are complete (a stream-ordered
+** barrier) and all-reduces the two doubles afterwards, which also tells every
+** rank that its arena has been read.
+*/
+template <typename GradT>
+__global__ void __launch_bounds__(ANNI_THREADS, 4) reduce_norm_kernel(const anni_launch a)
+{
+	constexpr int SLOTS = sizeof(GradT) == 2 ? 8 : 4;
+	__shared__ int s_last;
+	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_CHUNK_LOG2);
+	const uint64_t t8 = (uint64_t)threadIdx.x * ANNI_VEC;
+	const int np = a.n_peers;
+	const bool pow2 = (np & (np - 1)) == 0 && np <= SLOTS;
+	const int lg = np == 1 ? 0 : np == 2 ? 1 : np == 4 ? 2 : 3;
+	const int cb = pow2 ? SLOTS >> lg : 0;		/* chunks per batch */
+	double acc0 = 0.0;
+	double acc1 = 0.0;
+	uint64_t it = 0;
+	double s;
+
+	if (a.aligned && cb > 0) {
+		for (; it + cb <= w.iters; it += cb) {
+			raw8<GradT> r[SLOTS];
+			uint64_t cmax = 0;
+
+			for (int ci = 0; ci < cb; ci++)
+				cmax = max(cmax, walk_chunk(w, it + ci));
+			if ((cmax + 1) * ANNI_CHUNK > a.n)
+				break;
+#pragma unroll
+			for (int sl = 0; sl < SLOTS; sl++)
+				r[sl].load(a.peer_grad[sl & (np - 1)], walk_chunk(w, it + (sl >> lg)) * ANNI_CHUNK + t8);
+#pragma unroll
+			for (int ci = 0; ci < SLOTS; ci++)
+				if (ci < cb) {
+					if (np == 1)
+						reduce_store<GradT, SLOTS>(a, r, ci, walk_chunk(w, it + ci) * ANNI_CHUNK + t8, acc0, acc1);
+					else if (np == 2 && ci < SLOTS / 2)
+						reduce_store<GradT, SLOTS>(a, r, ci * 2, walk_chunk(w, it + ci) * ANNI_CHUNK + t8, acc0, acc1);
+					else if (np == 4 && ci < SLOTS / 4)
+						reduce_store<GradT, SLOTS>(a, r, ci * 4, walk_chunk(w, it + ci) * ANNI_CHUNK + t8, acc0, acc1);
+					else if (np == 8 && ci < SLOTS / 8)
+						reduce_store<GradT, SLOTS>(a, r, 0, walk_chunk(w, it + ci) * ANNI_CHUNK + t8, acc0, acc1);
+				}
+		}
+	}
+	for (; it < w.iters; it++) {		/* what is left, chunk by chunk, any peer count */
+		const uint64_t c = walk_chunk(w, it);
+		const uint64_t e = c * ANNI_CHUNK + t8;
+
+		if (c >= w.chunks)
+			continue;
+		for (int j = 0; j < ANNI_VEC; j++)
+			if (e + j < a.n) {
+				float x = io8<GradT>::load1(a.peer_grad[0], e + j);
+
+				for (int k = 1; k < np; k++)
+					x = __fadd_rn(x, io8<GradT>::load1(a.peer_grad[k], e + j));
+				io8<GradT>::store1(a.grad, e + j, x);
+				x = io8<GradT>::load1(a.grad, e + j);
+				acc0 = fma((double)x, (double)x, acc0);
+			}
+	}
+	s = block_sum(acc0 + acc1);
+	if (threadIdx.x == 0) {
+		a.ctl->partials[blockIdx.x] = s;
+		__threadfence();
+		s_last = atomicAdd(&a.ctl->norm_ticket, 1u) == gridDim.x - 1;
+	}
+	__syncthreads();
+	if (s_last) {
 		double t;
 
 		__threadfence();
@@ -986,6 +1174,18 @@ extern "C" int anni_launch_norm(const anni_launch *a, int grad_dtype, int blocks
 		norm_kernel<__nv_bfloat16><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	else
 		norm_kernel<float><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+extern "C" int anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st)
+{
+	if (!a || blocks < 1 || blocks > ANNI_MAX_BLOCKS || a->n_peers < 1 || a->n_peers > ANNI_MAX_PEERS)
+		return ANNI_E_ARG;
+	if (grad_dtype == ANNI_DT_BF16)
+		reduce_norm_kernel<__nv_bfloat16><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	else
+		reduce_norm_kernel<float><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	anni_count_launch();
 	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }

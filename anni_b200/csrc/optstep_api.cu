@@ -229,6 +229,48 @@ extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp
 	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
 }
 
+extern "C" int anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad,
+	void *const *peer_twin, void *const *peer_twin_fp8, int n_peers, uint64_t arena_off_padded)
+{
+	const size_t gsz = h && h->cfg.grad_dtype == ANNI_DT_BF16 ? 2u : 4u;
+	uintptr_t bits = 0;
+	int k;
+
+	if (!h || n_peers < 0 || n_peers > ANNI_MAX_PEERS)
+		return ANNI_E_ARG;
+	if (n_peers == 0) {
+		h->la.n_peers = 0;
+		return ANNI_OK;
+	}
+	if (!peer_grad || !peer_twin || (h->has_fp8 && !peer_twin_fp8))
+		return ANNI_E_ARG;
+	for (k = 0; k < n_peers; k++) {
+		if (!peer_grad[k] || !peer_twin[k] || (h->has_fp8 && !peer_twin_fp8[k]))
+			return ANNI_E_ARG;
+		h->la.peer_grad[k] = (const char *)peer_grad[k] + arena_off_padded * gsz;
+		h->la.twin_peer[k] = (uint16_t *)peer_twin[k] + arena_off_padded;
+		h->la.twin8_peer[k] = h->has_fp8 ? (uint8_t *)peer_twin_fp8[k] + arena_off_padded : NULL;
+		bits |= (uintptr_t)h->la.peer_grad[k] | (uintptr_t)h->la.twin_peer[k]
+		    | (uintptr_t)h->la.twin8_peer[k];
+	}
+	if (bits & 15)
+		return ANNI_E_ARG;	/* peer arenas and the shard offset must keep 16-byte alignment */
+	h->la.n_peers = n_peers;
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
+{
+	anni_launch la;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	if (la.n_peers < 1)
+		return ANNI_E_ARG;
+	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_split, (cudaStream_t)stream);
+}
+
 extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
 {
 	anni_launch la;

@@ -24,6 +24,7 @@
 #define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
 #define ANNI_UCHUNK_LOG2	10
 #define ANNI_MAX_BLOCKS		2048	/* capacity of the per-block partial table */
+#define ANNI_MAX_PEERS		8	/* GPUs of one NVSwitch domain */
 /* polls of a bounded device wait before it gives up (each poll sleeps >= 32 ns) */
 #define ANNI_WAIT_POLLS		(1u << 23)
 
@@ -83,6 +84,17 @@ typedef struct anni_launch {
 	float		ibc2;		/* 1 / (1 - beta2^t) */
 	float		eps;
 	float		lrwd;		/* lr * weight_decay */
+	/*
+	** ZeRO-1 over peer memory (all NULL / 0 on one GPU).  peer_grad[k]: rank k's
+	** copy of THIS shard's gradients (its full gradient arena + this shard's
+	** offset), read by the fused reduce-scatter + norm kernel.  twin_peer[k]:
+	** where THIS shard's bf16 twins go inside rank k's full twin arena (this
+	** rank included), written by the update phase in place of an all-gather.
+	*/
+	const void	*peer_grad[ANNI_MAX_PEERS];
+	uint16_t	*twin_peer[ANNI_MAX_PEERS];
+	uint8_t		*twin8_peer[ANNI_MAX_PEERS];
+	int		n_peers;	/* world size when peer memory is in use, else 0 */
 	anni_control	*ctl;
 } anni_launch;
 
@@ -102,6 +114,7 @@ int	anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, in
 int	anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
 		cudaStream_t st);
 int	anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st);
+int	anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
 int	anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st);
 int	anni_launch_axpy(float *y, const float *x, float a, uint64_t n, cudaStream_t st);
 /* Persistent-grid size for the given kernel family on the current device. */

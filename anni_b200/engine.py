@@ -226,6 +226,18 @@ class OptStep:
     def update(self, hp, stream=None):
         check("anni_optstep_update", self.L.anni_optstep_update(self.h, C.byref(hp), self._stream(stream)))
 
+    def set_peers(self, peer_grad, peer_twin, peer_twin_fp8, arena_off_padded):
+        """Peer-accessible device pointers (ints) of every rank's full gradient / twin arenas."""
+        n = len(peer_grad)
+        arr = lambda xs: (C.c_void_p * n)(*[C.c_void_p(int(x)) for x in xs]) if xs else None
+        check("anni_optstep_set_peers",
+              self.L.anni_optstep_set_peers(self.h, arr(peer_grad), arr(peer_twin), arr(peer_twin_fp8),
+                                            n, int(arena_off_padded)))
+
+    def reduce_norm(self, hp, stream=None):
+        check("anni_optstep_reduce_norm",
+              self.L.anni_optstep_reduce_norm(self.h, C.byref(hp), self._stream(stream)))
+
     def quantize(self, stream=None):
         check("anni_optstep_quantize", self.L.anni_optstep_quantize(self.h, self._stream(stream)))
 

@@ -19,6 +19,21 @@ the all-gather); rank r owns master / m / v of shard r only.  Per step::
 
 ``torch.distributed`` (NCCL over NVLink / NVSwitch) is the plumbing; the arithmetic is
 in ``libanni_b200.so``.  The collectives see only this process's own device memory.
+
+Peer mode (``peer=True``, the default on GPUs when symmetric memory is available): the
+two big collectives disappear into the kernels.  The gradient and twin arenas live in
+symmetric memory (``torch.distributed._symmetric_memory``); ``reduce_norm`` reads this
+rank's shard out of every peer's gradient arena over NVLink, reduces it and computes the
+norm in one pass, and the update kernel stores its twins straight into every peer's twin
+arena.  What is left for NCCL is the two-double all-reduce (which doubles as the "my arena
+has been read" barrier) and one small barrier at the end of the step::
+
+    [barrier: every rank's gradients are complete]
+    reduce_norm kernel   peer loads + sum + round + local store + sum of squares
+    all_reduce(sum)      2 doubles
+    update kernel        decision + AdamW + twins stored into all ranks' arenas
+    [all_reduce(max) of amax; quantise kernel with peer stores]      (fp8 twins only)
+    barrier              every rank's twins have landed
 """
 import torch
 import torch.distributed as dist
@@ -50,7 +65,7 @@ class Zero1:
     """
 
     def __init__(self, segments, *, grad_dtype=DT_BF16, state_dtype=DT_F32, group=None,
-                 device=None, make_stepper=None):
+                 device=None, make_stepper=None, peer=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -72,10 +87,24 @@ class Zero1:
         # an empty shard still takes part in every collective; it sits at the arena end
         self.eng = make_stepper(min(self.shard_off, self.n_arena), self.shard_n)
         gdt, sdt, dev = _TORCH_DT[grad_dtype], _TORCH_DT[state_dtype], self.device
-        self.grad_full = torch.zeros(self.padded, dtype=gdt, device=dev)
-        self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
-        self.twin8_full = (torch.zeros(self.padded, dtype=torch.uint8, device=dev)
-                           if self.eng.has_fp8 else None)
+        self._gdt = gdt
+        if peer is None:
+            peer = self.world > 1 and dev.type == "cuda" and hasattr(self.eng, "set_peers")
+        self.peer = bool(peer) and self.world > 1
+        self._tiny = torch.zeros(1, dtype=torch.float32, device=dev)
+        if self.peer:
+            self.grad_full, self._peer_grad = self._symm(self.padded, gdt)
+            self.twin_full, self._peer_twin = self._symm(self.padded, torch.bfloat16)
+            if self.eng.has_fp8:
+                self.twin8_full, self._peer_twin8 = self._symm(self.padded, torch.uint8)
+            else:
+                self.twin8_full, self._peer_twin8 = None, None
+            self.eng.set_peers(self._peer_grad, self._peer_twin, self._peer_twin8, self.rank * self.per)
+        else:
+            self.grad_full = torch.zeros(self.padded, dtype=gdt, device=dev)
+            self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
+            self.twin8_full = (torch.zeros(self.padded, dtype=torch.uint8, device=dev)
+                               if self.eng.has_fp8 else None)
         lo, hi = self.rank * self.per, (self.rank + 1) * self.per
         self.master = torch.zeros(self.per, dtype=torch.float32, device=dev)
         self.m = torch.zeros(self.per, dtype=sdt, device=dev)
@@ -88,6 +117,36 @@ class Zero1:
         self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard,
                       self.twin8_shard)
         self.timing = None
+
+    # -- peer memory ----------------------------------------------------------------------
+    def _symm(self, n, dtype):
+        """A zeroed arena in symmetric memory and every rank's device pointer to its copy."""
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(n, dtype=dtype, device=self.device)
+        t.zero_()
+        hdl = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+        return t, [int(p) for p in hdl.buffer_ptrs]
+
+    def new_grad_arena(self):
+        """Another full gradient arena (e.g. one per micro-step buffer); see use_grad_arena."""
+        if self.peer:
+            return self._symm(self.padded, self._gdt)
+        return torch.zeros(self.padded, dtype=self._gdt, device=self.device), None
+
+    def use_grad_arena(self, arena):
+        """Make (tensor, peer pointers) from new_grad_arena the input of the next steps."""
+        t, ptrs = arena
+        self.grad_full = t
+        if self.peer:
+            self._peer_grad = ptrs
+            self.eng.set_peers(self._peer_grad, self._peer_twin, self._peer_twin8, self.rank * self.per)
+        elif self.world == 1:
+            self.grad_shard = t[:self.per]
+            self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard, self.twin8_shard)
+
+    def _barrier(self):
+        """Stream-ordered barrier across the ranks (a one-float all-reduce)."""
+        dist.all_reduce(self._tiny, group=self.group)
 
     # -- state in / out (arena order, full arrays; used by tests and checkpoints) -------
     def load_shard_from_full(self, master_full, m_full, v_full):
@@ -106,13 +165,30 @@ class Zero1:
         return out[:self.n_arena]
 
     # -- the step ------------------------------------------------------------------------
-    def step(self, hp, record=None):
+    def step(self, hp, record=None, grads_complete=False):
         """One sharded step.  ``record`` (optional) is called with a phase name after each
-        phase has been queued, so a caller can drop timing events between them."""
+        phase has been queued, so a caller can drop timing events between them.
+        ``grads_complete``: every rank's gradient arena was complete before the previous
+        step's closing barrier (peer mode then skips the opening barrier)."""
         mark = record if record is not None else (lambda name: None)
         if self.world == 1 and hasattr(self.eng, "step"):
             self.eng.step(hp)           # nothing to exchange: the single cooperative launch
             mark("step")
+            return
+        if self.peer:
+            if not grads_complete:
+                self._barrier()
+            self.eng.reduce_norm(hp)
+            mark("reduce_scatter+norm")
+            dist.all_reduce(self.eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)
+            mark("all_reduce")
+            self.eng.update(hp)
+            if self.eng.has_fp8:
+                dist.all_reduce(self.eng.amax_tensor(), op=dist.ReduceOp.MAX, group=self.group)
+                self.eng.quantize()
+            mark("update+all_gather")
+            self._barrier()
+            mark("barrier")
             return
         if self.world > 1:
             dist.reduce_scatter_tensor(self.grad_shard, self.grad_full, op=dist.ReduceOp.SUM,

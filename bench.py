@@ -34,9 +34,9 @@ N_PARAMS = 555_762_080
 ALG_BYTES_PER_PARAM = 20     # bf16 grad 2 + fp32 master r/w 8 + bf16 m r/w 4 + bf16 v r/w 4 + bf16 twin 2
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0)
 # DRAM bytes per parameter of the fused kernel from the ncu capture summarised in
-# profiles/fused_kernel_bf16state.md (dram__bytes_read.sum + dram__bytes_write.sum of a
+# profiles/fused_kernel_bf16state_100M.md (dram__bytes_read.sum + dram__bytes_write.sum of a
 # 100.7M-parameter launch; traffic grows in proportion to the parameter count).
-NCU_DRAM_BYTES_PER_PARAM = 23.3
+NCU_DRAM_BYTES_PER_PARAM = 22.95
 
 
 def measured_peaks():
@@ -205,19 +205,18 @@ def run_ours(args):
     z.v.copy_(torch.randn(z.per, device=dev, generator=gen).mul_(1e-6).abs_())
 
     K, W = args.steps, args.warmup
-    pool_n = min(K + W, 48)
-    pool = [torch.empty(z.padded, dtype=torch.bfloat16, device=dev) for _ in range(pool_n)]
+    # one rank: the step consumes (zeroes) its gradient arena, so every step gets a fresh one;
+    # several ranks: the arenas are only read (the reduced shard is what gets zeroed): four, cycled
+    pool_n = min(K + W, 48) if world == 1 else 4
+    pool = [z.new_grad_arena() for _ in range(pool_n)]
 
     def refill():
-        for i, b in enumerate(pool):
+        for i, (b, _) in enumerate(pool):
             b.zero_()
             fill_grads(b, n, 1000 * rank + i, dev)
 
-    def bind_grads(buf):
-        z.grad_full = buf
-        if world == 1:
-            z.grad_shard = buf[:z.per]
-            z.eng.bind(z.master, z.m, z.v, z.grad_shard, z.twin_shard, z.twin8_shard)
+    def bind_grads(arena):
+        z.use_grad_arena(arena)
 
     def hyper(t, exact=False):
         return OptStep.hyper(lr=HYPER["lr"], t=t, beta1=HYPER["beta1"], beta2=HYPER["beta2"],
@@ -240,13 +239,18 @@ def run_ours(args):
         z.step(hyper(t))
         t += 1
         done += 1
+    if world > 1:
+        done = 0            # arenas are not consumed: no refills between batches
     total_ms, launches0 = 0.0, kernel_launches()
     phase_ms = {}
     left = K
     wall0 = time.time()
     while left > 0:
-        batch = min(left, pool_n - (done % pool_n)) if done % pool_n else min(left, pool_n)
-        if done % pool_n == 0 and done > 0:
+        if world > 1:
+            batch = left
+        else:
+            batch = min(left, pool_n - (done % pool_n)) if done % pool_n else min(left, pool_n)
+        if world == 1 and done % pool_n == 0 and done > 0:
             refill()
         barrier()
         e0 = torch.cuda.Event(enable_timing=True)
@@ -263,7 +267,7 @@ def run_ours(args):
                     e = torch.cuda.Event(enable_timing=True)
                     e.record()
                     evs.append((name, e))
-                z.step(hyper(t), record=rec)
+                z.step(hyper(t), record=rec, grads_complete=True)
                 marks.append(evs)
             else:
                 z.step(hyper(t))
@@ -312,16 +316,13 @@ def run_ours(args):
     # ---- e2e: host gradient buffers through the C ABI --------------------------------------
     e2e_steps = max(2, min(5, K))
     host = [torch.empty(z.padded, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    tmp = torch.zeros(z.padded, dtype=torch.bfloat16, device=dev)
     for i, hb in enumerate(host):
-        hb.copy_(pool[i % pool_n])
-        if not bool(hb[:1024].float().abs().sum() > 0):      # pool entry already consumed (zeroed)
-            tmp = torch.empty(z.padded, dtype=torch.bfloat16, device=dev)
-            tmp.zero_()
-            fill_grads(tmp, n, 777 + i + 10 * rank, dev)
-            hb.copy_(tmp)
-            del tmp
-    dgrad = pool[0]
-    bind_grads(dgrad)
+        fill_grads(tmp, n, 777 + i + 10 * rank, dev)
+        hb.copy_(tmp)
+    del tmp
+    dgrad = pool[0][0]
+    bind_grads(pool[0])
     barrier()
     w0 = time.perf_counter()
     for i in range(e2e_steps):
@@ -344,7 +345,8 @@ def run_ours(args):
     clocks = sampler.finish(wall0, wall1) if sampler else None
     peak, peak_kind = measured_peaks()
     # the dominant kernel's share of the step: at N = 1 the step IS one launch of it
-    kern_ms = ms_per_step if world == 1 else phase_ms.get("update", 0.0) / K
+    upd_key = "update+all_gather" if "update+all_gather" in phase_ms else "update"
+    kern_ms = ms_per_step if world == 1 else phase_ms.get(upd_key, 0.0) / K
     shard_n = z.shard_n
     achieved = ALG_BYTES_PER_PARAM * shard_n / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None
     line = {
@@ -373,6 +375,15 @@ def run_ours(args):
     }
     if world > 1:
         line["phases_ms"] = {k: v / K for k, v in phase_ms.items()}
+        wire = (world - 1) / world * n * 2 / 1e9            # GB each way per GPU, per collective
+        rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
+        ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
+        line["nvlink"] = {"mode": "peer kernels" if z.peer else "nccl", "wire_gb_per_collective": wire,
+                          "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,
+                          "reduce_scatter_frac": (wire / 770.0 * 1e3) / rs_ms if rs_ms else None,
+                          "all_gather_frac": (wire / 770.0 * 1e3) / ag_ms if ag_ms else None}
+        line["roofline"]["kernel"] = ("update_kernel<bf16,bf16> with peer twin stores" if z.peer
+                                      else "update_kernel<bf16,bf16>")
     if world == 1:
         line["exact_update"] = {"ms_per_step": exact_ms, "value": n / (exact_ms * 1e-3),
                                 "roofline_frac": ALG_BYTES_PER_PARAM * n / (exact_ms * 1e-3) / 1e9 / peak,

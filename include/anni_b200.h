@@ -164,6 +164,31 @@ double	*anni_optstep_reduce_buffer(anni_optstep *h);	/* device double[2] */
 float	*anni_optstep_amax_buffer(anni_optstep *h);	/* device float[n_seg] */
 float	*anni_optstep_scale_buffer(anni_optstep *h);	/* device float[n_seg]: dequantisation scales */
 
+/*
+** ZeRO-1 over peer memory (NVLink / NVSwitch), no counterpart in the reference
+** (it is single-GPU).  Instead of an NCCL reduce-scatter before and an
+** all-gather after the step, the kernels themselves move the data:
+**   anni_optstep_set_peers   peer_grad[k]  = rank k's FULL gradient arena (element 0 of the
+**                            padded arena), peer_twin[k] / peer_twin_fp8[k] = rank k's FULL
+**                            twin arenas; all peer-accessible device pointers valid in this
+**                            process (e.g. CUDA IPC or symmetric memory), n_peers = world
+**                            size <= 8, arena_off_padded = this shard's first element in
+**                            those padded arenas.  n_peers = 0 detaches.
+**   anni_optstep_reduce_norm replaces reduce-scatter + anni_optstep_norm: reads this shard from
+**                            every peer's arena, sums in rank order in float, writes the
+**                            reduced shard into the bound gradient buffer, leaves {sumsq,
+**                            nonfinite} in the reduce buffer.  Queue it after a barrier that
+**                            says every rank's gradients are complete.
+**   anni_optstep_update / anni_optstep_quantize then write the twins of this shard into every
+**                            peer's arena (this rank's included): queue a barrier after them
+**                            before anyone reads the twins.
+** The kernels contain no cross-GPU waits; ordering between ranks is the caller's (stream-ordered
+** collectives or events).
+*/
+int	anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad, void *const *peer_twin,
+		void *const *peer_twin_fp8, int n_peers, uint64_t arena_off_padded);
+int	anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
+
 /* Blocks until `stream` has finished the queued steps, then copies the status. */
 int	anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *stream);
 
