@@ -32,6 +32,16 @@ sys.path.insert(0, ROOT)
 WORKLOAD = "run555m"
 N_PARAMS = 555_762_080
 ALG_BYTES_PER_PARAM = 20     # bf16 grad 2 + fp32 master r/w 8 + bf16 m r/w 4 + bf16 v r/w 4 + bf16 twin 2
+# --workload selects another benchmark configuration for side measurements (the default, and the
+# only one the contract line is about, is run555m):
+#   name -> (shape, gradient dtype, moment dtype, twin kind, algorithmic bytes per parameter)
+WORKLOADS = {
+    "run555m": ("run555m", "bf16", "bf16", "bf16", 20),          # configuration 3
+    "run555m-fp8": ("run555m", "bf16", "bf16", "fp8", 19),       # configuration 5 (e4m3 twins for the block matrices)
+    "talk170m-mixed": ("talk170m", "bf16", "f32", "bf16", 28),   # configuration 2
+    "talk170m-fp32": ("talk170m", "f32", "f32", "bf16", 30),     # configuration 1 run on the GPU
+    "synth3b": ("synth3b", "bf16", "f32", "bf16", 28),           # configuration 4 (8 GPUs)
+}
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0)
 # DRAM bytes per parameter of the fused kernel from the ncu capture summarised in
 # profiles/fused_kernel_bf16state_100M.md (dram__bytes_read.sum + dram__bytes_write.sum of a
@@ -194,10 +204,14 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    segs = lm_segments(**LM_SHAPES[WORKLOAD], wd="matrices", twin="bf16")
+    shape, gdt_name, sdt_name, twin_kind, alg_bytes = WORKLOADS[args.workload]
+    from anni_b200.capi import DT_F32
+    gdt = DT_BF16 if gdt_name == "bf16" else DT_F32
+    sdt = DT_BF16 if sdt_name == "bf16" else DT_F32
+    segs = lm_segments(**LM_SHAPES[shape], wd="matrices", twin=twin_kind)
     n = segs.n
-    assert n == N_PARAMS
-    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=DT_BF16, device=dev)
+    assert args.workload != WORKLOAD or n == N_PARAMS
+    z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     z.master.normal_(0, 0.02, generator=gen)
@@ -207,7 +221,7 @@ def run_ours(args):
     K, W = args.steps, args.warmup
     # one rank: the step consumes (zeroes) its gradient arena, so every step gets a fresh one;
     # several ranks: the arenas are only read (the reduced shard is what gets zeroed): four, cycled
-    pool_n = min(K + W, 48) if world == 1 else 4
+    pool_n = min(K + W, 48 if n < 1_000_000_000 else 8) if world == 1 else 4
     pool = [z.new_grad_arena() for _ in range(pool_n)]
 
     def refill():
@@ -315,8 +329,8 @@ def run_ours(args):
 
     # ---- e2e: host gradient buffers through the C ABI --------------------------------------
     e2e_steps = max(2, min(5, K))
-    host = [torch.empty(z.padded, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    tmp = torch.zeros(z.padded, dtype=torch.bfloat16, device=dev)
+    host = [torch.empty(z.padded, dtype=z.grad_full.dtype).pin_memory() for _ in range(2)]
+    tmp = torch.zeros(z.padded, dtype=z.grad_full.dtype, device=dev)
     for i, hb in enumerate(host):
         fill_grads(tmp, n, 777 + i + 10 * rank, dev)
         hb.copy_(tmp)
@@ -348,26 +362,27 @@ def run_ours(args):
     upd_key = "update+all_gather" if "update+all_gather" in phase_ms else "update"
     kern_ms = ms_per_step if world == 1 else phase_ms.get(upd_key, 0.0) / K
     shard_n = z.shard_n
-    achieved = ALG_BYTES_PER_PARAM * shard_n / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None
+    achieved = alg_bytes * shard_n / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None
     line = {
         "metric": "adam_step_params_per_s", "value": value, "unit": "params/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64+f32",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "n_params": n, "grads": "bf16", "master": "fp32",
-                   "moments": "bf16", "twins": "bf16", "clip": HYPER["clip"], "wd": "0.1 on matrices",
+        "config": {"workload": args.workload, "n_params": n, "grads": gdt_name, "master": "fp32",
+                   "moments": sdt_name, "twins": twin_kind, "clip": HYPER["clip"], "wd": "0.1 on matrices",
+                   "alg_bytes_per_param": alg_bytes,
                    "update_arithmetic": "double moments, float update (fast mode)",
                    "zero_grad": True, "zero1_ranks": world,
                    "l2": "inputs larger than L2 (6.7 GB state + a fresh 1.1 GB gradient arena per step)",
-                   "hbm_gbs_alg": (ALG_BYTES_PER_PARAM * n / (ms_per_step * 1e-3) / 1e9)},
+                   "hbm_gbs_alg": (alg_bytes * n / (ms_per_step * 1e-3) / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak if achieved else None,
-                     "traffic": NCU_DRAM_BYTES_PER_PARAM * shard_n,
-                     "kernel": "fused_kernel<bf16,bf16>" if world == 1 else "update_kernel<bf16,bf16>",
+                     "traffic": NCU_DRAM_BYTES_PER_PARAM * shard_n if args.workload == WORKLOAD else None,
+                     "kernel": f"fused_kernel<{gdt_name},{sdt_name}>" if world == 1 else f"update_kernel<{gdt_name},{sdt_name}>",
                      "kernel_ms": kern_ms, "peak_kind": f"of {peak_kind}",
                      "frac_of_8000": achieved / 8000.0 if achieved else None},
         "e2e": {"value": e2e_value, "unit": "params/s",
-                "h2d_bytes_per_step": int(z.padded * 2), "d2h_bytes_per_step": 48,
+                "h2d_bytes_per_step": int(z.padded * z.grad_full.element_size()), "d2h_bytes_per_step": 48,
                 "steps": e2e_steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
@@ -382,11 +397,11 @@ def run_ours(args):
                           "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,
                           "reduce_scatter_frac": (wire / 770.0 * 1e3) / rs_ms if rs_ms else None,
                           "all_gather_frac": (wire / 770.0 * 1e3) / ag_ms if ag_ms else None}
-        line["roofline"]["kernel"] = ("update_kernel<bf16,bf16> with peer twin stores" if z.peer
-                                      else "update_kernel<bf16,bf16>")
+        if z.peer:
+            line["roofline"]["kernel"] += " with peer twin stores"
     if world == 1:
         line["exact_update"] = {"ms_per_step": exact_ms, "value": n / (exact_ms * 1e-3),
-                                "roofline_frac": ALG_BYTES_PER_PARAM * n / (exact_ms * 1e-3) / 1e9 / peak,
+                                "roofline_frac": alg_bytes * n / (exact_ms * 1e-3) / 1e9 / peak,
                                 "note": "same step with ANNI_STEP_EXACT_UPDATE (update term in double)"}
         base, _ = cpu_reference_step_rate(64 * 1024 * 1024, 3, 1)
         line["cpu_baseline"] = base
@@ -402,6 +417,7 @@ def main():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS))
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
