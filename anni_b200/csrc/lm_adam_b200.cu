@@ -139,6 +139,8 @@ extern "C" anni_lm_adam *anni_lm_adam_create(const anni_lm_tensor *tensors, int 
 	opt->eps = 1e-8;
 	opt->grad_dtype = grad_dtype;
 	opt->state_dtype = state_dtype;
+	/* the double-precision update term costs nothing next to fp32 moments, ~11 % next to bf16 ones */
+	opt->exact_update = state_dtype == ANNI_DT_F32;
 	opt->h_m = (float *)calloc((size_t)(off > 0 ? off : 1), sizeof(float));
 	opt->h_v = (float *)calloc((size_t)(off > 0 ? off : 1), sizeof(float));
 	if (!opt->h_m || !opt->h_v || opt->n_segs == 0) {
@@ -423,6 +425,8 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	hp.grad_scale = opt->loss_scale > 0.0 ? grad_scale / opt->loss_scale : grad_scale;
 	hp.t = opt->t;
 	hp.flags = ANNI_STEP_ZERO_GRAD;
+	if (opt->exact_update)
+		hp.flags |= ANNI_STEP_EXACT_UPDATE;
 	/* the reference computes the norm (and may skip) only when it clips (lm_adam.c:466) */
 	if (opt->grad_clip > 0.0 || opt->loss_scale > 0.0)
 		hp.flags |= ANNI_STEP_CHECK_FINITE;

@@ -77,6 +77,7 @@ typedef struct anni_lm_adam {
 	int		last_skipped;
 	int		last_error;	/* ANNI_E_* of the last step, 0 if it ran */
 	double		loss_scale;	/* > 0: gradients arrive multiplied by this; folded into grad_scale */
+	int		exact_update;	/* 1: ANNI_STEP_EXACT_UPDATE (default with fp32 moments) */
 	anni_optstep	*engine;
 } anni_lm_adam;
 

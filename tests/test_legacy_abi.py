@@ -191,7 +191,8 @@ class LmAdam(C.Structure):
                 ("d_v", C.c_void_p), ("dev_mv", C.c_int), ("params_valid", C.c_int),
                 ("offload_mv", C.c_int), ("weight_decay", d), ("grad_clip", d), ("last_grad_norm", d),
                 ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("last_skipped", C.c_int),
-                ("last_error", C.c_int), ("loss_scale", d), ("engine", C.c_void_p)]
+                ("last_error", C.c_int), ("loss_scale", d), ("exact_update", C.c_int),
+                ("engine", C.c_void_p)]
 
 
 def _mirror():
