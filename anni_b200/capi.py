@@ -66,6 +66,8 @@ def lib():
     L.anni_optstep_set_peers.argtypes = [vp, vp, vp, vp, i, C.c_uint64]
     L.anni_optstep_reduce_norm.restype = i
     L.anni_optstep_reduce_norm.argtypes = [vp, C.POINTER(Hyper), vp]
+    L.anni_optstep_selftest_barrier_timeout.restype = i
+    L.anni_optstep_selftest_barrier_timeout.argtypes = [vp, C.c_uint, vp]
     L.anni_optstep_quantize.restype = i
     L.anni_optstep_quantize.argtypes = [vp, vp]
     for name in ("anni_optstep_reduce_buffer", "anni_optstep_amax_buffer",

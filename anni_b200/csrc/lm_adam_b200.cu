@@ -469,6 +469,65 @@ fail:
 	return rc;
 }
 
+/* ---- gradient-buffer helpers (lang/gradutil.c of the reference) ---------------------------- */
+
+static size_t mat_bytes(const anni_mat *m)
+{
+	return (size_t)m->rows * (size_t)m->cols * sizeof(float);
+}
+
+/* mat_zero (gradutil.c:8-22): zero whichever side is authoritative. */
+extern "C" void anni_mat_zero(anni_mat *m)
+{
+	if (!m)
+		return;
+	if (m->d_data && m->on_device != 0 && gpu_available() && gpu_memset(m->d_data, 0, mat_bytes(m)) == 0) {
+		if (m->on_device != 3)
+			m->on_device = 1;	/* device-authoritative; an aliased view stays aliased */
+		return;
+	}
+	if (!m->data)
+		return;
+	memset(m->data, 0, mat_bytes(m));
+	m->on_device = 0;
+}
+
+/* mat_zero_dev (gradutil.c:29-50): zero host and device twin together; an aliased view stays aliased. */
+extern "C" void anni_mat_zero_dev(anni_mat *m)
+{
+	if (!m)
+		return;
+	if (m->d_data && gpu_available() && gpu_memset(m->d_data, 0, mat_bytes(m)) == 0) {
+		if (m->on_device == 3)
+			return;
+		if (m->data) {
+			memset(m->data, 0, mat_bytes(m));
+			m->on_device = 2;
+		} else
+			m->on_device = 1;
+		return;
+	}
+	if (!m->data)
+		return;
+	memset(m->data, 0, mat_bytes(m));
+	m->on_device = 0;
+}
+
+/* vec_zero (gradutil.c:52-56). */
+extern "C" void anni_vec_zero(anni_vec *v)
+{
+	if (v && v->data)
+		memset(v->data, 0, (size_t)v->n * sizeof(float));
+}
+
+/* mat_axpy (gradutil.c:58-75), device part only: 0 when y += a x ran on the GPU, else ANNI_E_*. */
+extern "C" int anni_mat_axpy(anni_mat *y, double a, const anni_mat *x)
+{
+	if (!y || !x || y->rows != x->rows || y->cols != x->cols)
+		return ANNI_E_ARG;
+	return gpu_mat_axpy(y, a, x) == 0 ? ANNI_OK : ANNI_E_CUDA;
+}
+
 /* ---- LR schedule ---------------------------------------------------------------------- */
 
 extern "C" double anni_lr_schedule(double base_lr, int step, int warmup_steps, int decay_steps,

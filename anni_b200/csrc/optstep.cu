@@ -331,7 +331,8 @@ __device__ __forceinline__ double block_sum(double v)
 ** which case the block records the error and the kernel returns without
 ** touching the parameters.  Returns false on timeout (uniform over the block).
 */
-__device__ __forceinline__ bool grid_barrier(anni_control *ctl, uint32_t target)
+__device__ __forceinline__ bool grid_barrier(anni_control *ctl, uint32_t target,
+	uint32_t max_polls = ANNI_WAIT_POLLS)
 {
 	__shared__ int s_ok;
 
@@ -344,7 +345,7 @@ __device__ __forceinline__ bool grid_barrier(anni_control *ctl, uint32_t target)
 		atomicAdd(&ctl->bar_count, 1u);
 		while (ld_acquire_u32(&ctl->bar_count) < target) {
 			__nanosleep(32);
-			if (++polls > ANNI_WAIT_POLLS) {
+			if (++polls > max_polls) {
 				ok = 0;
 				atomicExch(&ctl->error, ANNI_E_BARRIER_TIMEOUT);
 				break;
@@ -1024,6 +1025,19 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) quantize_kernel(const anni_la
 	quantize_phase(a);
 }
 
+/*
+** Failure-path self-test: every block arrives at a barrier that expects one
+** arrival more than the grid has, so the bounded wait must run out.  Nothing
+** faults and nothing hangs: after `max_polls` polls each block records
+** ANNI_E_BARRIER_TIMEOUT and returns, exactly as a block of the fused kernel
+** would if a peer block never arrived.
+*/
+__global__ void __launch_bounds__(ANNI_THREADS) barrier_timeout_kernel(anni_control *ctl, uint32_t max_polls)
+{
+	if (grid_barrier(ctl, gridDim.x + 1, max_polls) && threadIdx.x == 0)
+		atomicExch(&ctl->error, ANNI_E_ARG);	/* the barrier must not have opened */
+}
+
 /* One-shot fp32 -> bf16 of a flat buffer (seeding the twin; num/gpu.h:73 of the reference). */
 __global__ void __launch_bounds__(ANNI_THREADS) f32_to_bf16_kernel(uint16_t *dst, const float *src,
 	uint64_t n, int aligned)
@@ -1224,6 +1238,15 @@ extern "C" int anni_launch_fused(const anni_launch *a, int grad_dtype, int state
 	if (sb)
 		return launch_fused_t<float, __nv_bfloat16>(a, blocks, st);
 	return launch_fused_t<float, float>(a, blocks, st);
+}
+
+extern "C" int anni_launch_barrier_timeout(anni_control *ctl, int blocks, unsigned max_polls, cudaStream_t st)
+{
+	if (!ctl || blocks < 1 || blocks > ANNI_MAX_BLOCKS || max_polls > ANNI_WAIT_POLLS)
+		return ANNI_E_ARG;
+	barrier_timeout_kernel<<<blocks, ANNI_THREADS, 0, st>>>(ctl, max_polls);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
 
 extern "C" int anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st)

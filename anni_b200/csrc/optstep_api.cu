@@ -284,6 +284,13 @@ extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
 	return anni_launch_quantize(&la, h->blocks_split, (cudaStream_t)stream);
 }
 
+extern "C" int anni_optstep_selftest_barrier_timeout(anni_optstep *h, unsigned max_polls, void *stream)
+{
+	if (!h)
+		return ANNI_E_ARG;
+	return anni_launch_barrier_timeout(h->ctl, h->blocks_coop, max_polls, (cudaStream_t)stream);
+}
+
 extern "C" double *anni_optstep_reduce_buffer(anni_optstep *h)
 {
 	return h ? (double *)((char *)h->ctl + offsetof(anni_control, reduce)) : NULL;

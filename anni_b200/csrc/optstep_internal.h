@@ -114,6 +114,7 @@ int	anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, in
 int	anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
 		cudaStream_t st);
 int	anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st);
+int	anni_launch_barrier_timeout(anni_control *ctl, int blocks, unsigned max_polls, cudaStream_t st);
 int	anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
 int	anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st);
 int	anni_launch_axpy(float *y, const float *x, float a, uint64_t n, cudaStream_t st);

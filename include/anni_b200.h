@@ -225,6 +225,15 @@ int	anni_optstep_step_noalloc(const anni_optstep_config *cfg, const anni_optstep
 /* Status of the last no-alloc step on the current device (synchronises `stream`). */
 int	anni_optstep_status_noalloc(anni_optstep_status *out, void *stream);
 
+/*
+** Failure-path self-test of the bounded device wait: launches the engine's grid against a
+** barrier that expects one block more than exists, with a poll limit of `max_polls` (keep it
+** small: 65536 polls is a few milliseconds).  Every block gives up, nothing faults or hangs;
+** afterwards anni_optstep_status_read reports error == ANNI_E_BARRIER_TIMEOUT and re-arms the
+** engine, which then steps normally.  No counterpart in the reference.
+*/
+int	anni_optstep_selftest_barrier_timeout(anni_optstep *h, unsigned max_polls, void *stream);
+
 /* Launch geometry in use (blocks of the persistent grid, threads per block). */
 int	anni_optstep_grid(anni_optstep *h, int *blocks, int *threads);
 

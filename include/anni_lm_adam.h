@@ -26,6 +26,7 @@
 
 #include <stdint.h>
 #include "anni_b200.h"
+#include "anni_gpu_compat.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -102,6 +103,18 @@ void	anni_lm_adam_set_offload(int on);
 int	anni_lm_adam_upload_grads(anni_lm_adam *opt);
 /* Load m/v (fp32, arena order) e.g. from a checkpoint; uploaded at the next step. */
 int	anni_lm_adam_set_moments(anni_lm_adam *opt, const float *m, const float *v);
+
+/*
+** Gradient-buffer helpers of lang/gradutil.h on the reference's mat / vec layout: mat_zero
+** (gradutil.c:8), mat_zero_dev (:29: host and device twin together, an aliased view stays
+** aliased), vec_zero (:52), mat_axpy (:58; here the device part only -- there is no host loop).
+** The backward-pass GEMM wrappers of that header (mat_outer_add, mat_mul_at, mat_mul_wt*) are not
+** part of the optimizer step and are not provided.
+*/
+void	anni_mat_zero(anni_mat *m);
+void	anni_mat_zero_dev(anni_mat *m);
+void	anni_vec_zero(anni_vec *v);
+int	anni_mat_axpy(anni_mat *y, double a, const anni_mat *x);
 
 /* lm_train_step_lr (lang/lm_train.c:98-124): warm-up, then "none" | "linear" | cosine decay. */
 double	anni_lr_schedule(double base_lr, int step, int warmup_steps, int decay_steps,

@@ -128,6 +128,55 @@ def test_mat_axpy_on_device_twins():
     assert L.gpu_mat_axpy(C.byref(y), 1.0, C.byref(bad)) == -1  # shape mismatch -> CPU path
 
 
+def test_gradient_buffer_helpers():
+    """mat_zero / mat_zero_dev / vec_zero / mat_axpy of lang/gradutil.h on the reference's mat layout."""
+    class Mat(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("d_data", C.c_void_p), ("rows", C.c_int),
+                    ("cols", C.c_int), ("on_device", C.c_int)]
+
+    class Vec(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("n", C.c_int)]
+    L = _legacy()
+    for f in (L.anni_mat_zero, L.anni_mat_zero_dev):
+        f.argtypes = [C.POINTER(Mat)]
+        f.restype = None
+    L.anni_vec_zero.argtypes = [C.POINTER(Vec)]
+    L.anni_mat_axpy.restype = C.c_int
+    L.anni_mat_axpy.argtypes = [C.POINTER(Mat), d, C.POINTER(Mat)]
+    rows, cols = 19, 33
+    host = np.ones(rows * cols, np.float32)
+    dev = torch.ones(rows * cols, device="cuda")
+    m = Mat(host.ctypes.data, dev.data_ptr(), rows, cols, 1)          # device-authoritative
+    L.anni_mat_zero(C.byref(m))
+    L.gpu_device_sync()
+    assert not dev.any() and host.all() and m.on_device == 1         # only the authoritative side
+    host[:] = 1
+    dev.fill_(1)
+    m.on_device = 2
+    L.anni_mat_zero_dev(C.byref(m))
+    L.gpu_device_sync()
+    assert not dev.any() and not host.any() and m.on_device == 2     # both sides, still in sync
+    dev.fill_(1)
+    host[:] = 1
+    m.on_device = 3                                                   # aliased view into a flat
+    L.anni_mat_zero_dev(C.byref(m))
+    L.gpu_device_sync()
+    assert not dev.any() and host.all() and m.on_device == 3         # alias kept, host untouched
+    m.on_device = 0                                                   # host-authoritative
+    L.anni_mat_zero(C.byref(m))
+    assert not host.any() and m.on_device == 0
+    vh = np.ones(7, np.float32)
+    v = Vec(vh.ctypes.data, 7)
+    L.anni_vec_zero(C.byref(v))
+    assert not vh.any()
+    x = Mat(None, torch.full((rows * cols,), 2.0, device="cuda").data_ptr(), rows, cols, 1)
+    dev.fill_(1)
+    m.on_device = 1
+    assert L.anni_mat_axpy(C.byref(m), 0.5, C.byref(x)) == 0
+    L.gpu_device_sync()
+    assert bool((dev == 2.0).all())
+
+
 @pytest.mark.skipif(not os.path.exists(DROPIN), reason="oracle/_ref/libannref_dropin.so not built")
 @pytest.mark.parametrize("bf16_prec", [0, 1])
 def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec):

@@ -142,3 +142,34 @@ def test_exact_update_mode_is_bit_faithful(oracle, grad_dtype, state_dtype, t):
     assert d.max() <= 1, int(d.max())
     assert (d == 0).mean() >= 0.99999, float((d == 0).mean())
     assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"]))
+
+
+def test_bounded_wait_runs_out_and_engine_recovers(oracle):
+    """Failure detection without a fault: a barrier that cannot complete (it expects one block
+    more than the grid has) makes every block's bounded wait run out after a few milliseconds;
+    the host reads ANNI_E_BARRIER_TIMEOUT, the engine is re-armed, and the next real step is
+    correct."""
+    import ctypes as C
+    from anni_b200 import capi
+    from anni_b200.engine import OptStep
+    from parity_util import to_dev, to_host
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=8)
+    eng = OptStep(segs, grad_dtype=DT_F32, state_dtype=DT_F32).allocate()
+    for t_, a_ in ((eng.master, p), (eng.grad, g), (eng.m, m), (eng.v, v)):
+        t_.copy_(to_dev(a_))
+    rc = eng.L.anni_optstep_selftest_barrier_timeout(eng.h, 1 << 16, eng._stream(None))
+    assert rc == capi.OK
+    st = eng.status()
+    assert st.error == capi.E_BARRIER_TIMEOUT
+    assert np.array_equal(to_host(eng.master), p)              # nothing was touched
+    assert eng.status().error == 0                             # reading the status re-armed the engine
+    kw = dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t_before=3)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    eng.step(OptStep.hyper(**dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t=4)))
+    st = eng.status()
+    assert st.error == 0 and st.skipped == 0
+    out = dict(p=to_host(eng.master), m=to_host(eng.m), v=to_host(eng.v))
+    check_step(out, rp, rm, rv, p, exact_moments=not info["norm"] > 1.0)
+    eng.close()
