@@ -133,6 +133,48 @@ int	anni_ckpt_write_adam(const char *path, int append, int epoch, int step, int 
 int	anni_ckpt_read_adam(const char *path, int64_t offset, int64_t n_expected, int *epoch,
 		int *step, int *t, float *m, float *v);
 
+/*
+** Whole checkpoints of the reference trainer (weight section + Adam section,
+** lang/lm_serialize.c:103-126, :302-331, :526-587), in and out of the optimizer's flat order
+** (w_head, b_head, [embedding], blocks: lang/lm_adam.c:117-136).  kind: 0 = LMCF byte-level
+** model, 1 = LMCV (BPE merge table embedded), 2 = LMCT (BPE + tied embedding).  `merges` holds
+** n_merges {left, right} int32 pairs (lang/bpe.c:383-401); merges_word is the count as stored,
+** including the tokenizer's whitespace-runs flag bit.
+*/
+typedef struct anni_ckpt_model {
+	int	kind;
+	int	d_model;
+	int	n_heads;
+	int	d_ff;
+	int	max_ctx;
+	int	n_blocks;
+	int	vocab;
+	int	tied;
+	int	n_merges;
+	int	merges_word;
+	int64_t	n;		/* optimizer slots implied by the dimensions (lm_param_count) */
+	int	has_adam;
+	int	epoch;
+	int	step;
+	int	t;
+} anni_ckpt_model;
+
+/* Header, slot count and Adam header of a checkpoint file; nothing else is read. */
+int	anni_ckpt_probe(const char *path, anni_ckpt_model *info);
+/*
+** lm_load_checkpoint / lm_load: weights into w[info->n] in optimizer order, m and v (may be
+** NULL) likewise, the merge pairs into merges (may be NULL).  Shapes in the file must match the
+** header's dimensions, the Adam slot count must match the model.
+*/
+int	anni_ckpt_load(const char *path, anni_ckpt_model *info, float *w, float *m, float *v,
+		int32_t *merges);
+/*
+** lm_save_checkpoint (m, v given: has_adam = 1 with info's epoch, step, t) or lm_save (m = v =
+** NULL: has_adam = 0), byte-identical to the reference's files; written to PATH.tmp and renamed.
+*/
+int	anni_ckpt_save(const char *path, const anni_ckpt_model *info, const int32_t *merges,
+		const float *w, const float *m, const float *v);
+
 #ifdef __cplusplus
 }
 #endif

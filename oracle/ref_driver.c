@@ -221,3 +221,100 @@ int ref_seg_list(int vocab, int *off, int *n, int *is_vec, int cap)
 	lm_free(&model);
 	return ns;
 }
+
+/*
+** Full checkpoints (weight section + Adam section) of the three kinds the
+** reference writes (lang/lm_serialize.c:103-126): mode 0 = byte-level model
+** (LMCF), 1 = BPE tokenizer embedded (LMCV), 2 = BPE + tied embedding (LMCT).
+** The BPE table is synthetic: merge i joins tokens (VOCAB_SPECIALS + 2i) and
+** (VOCAB_SPECIALS + 2i + 1); only its byte layout matters here.  Weights are set
+** from w[] in OPTIMIZER order (the slot order of lm_adam_create) before saving.
+** *n_io = 0 only queries the slot count.
+*/
+#include "bpe.h"
+
+static lm *make_model(int mode, int n_merges)
+{
+	bpe *tok;
+	int *l;
+	int *r;
+	int i;
+	lm *model;
+
+	if (mode == 0)
+		return lm_create();
+	l = malloc((size_t)(n_merges ? n_merges : 1) * sizeof(int));
+	r = malloc((size_t)(n_merges ? n_merges : 1) * sizeof(int));
+	for (i = 0; i < n_merges; i++) {
+		l[i] = VOCAB_SPECIALS + (2 * i) % 256;
+		r[i] = VOCAB_SPECIALS + (2 * i + 1) % 256;
+	}
+	tok = bpe_create(l, r, n_merges);
+	free(l);
+	free(r);
+	if (!tok)
+		return NULL;
+	model = mode == 2 ? lm_create_bpe_tied(tok) : lm_create_bpe(tok);
+	if (!model)
+		bpe_free(&tok);
+	return model;
+}
+
+int ref_ckpt_save_full(const char *path, int mode, int n_merges, const float *w, const float *m,
+	const float *v, int *n_io, int t, int epoch, int step)
+{
+	lm *model = make_model(mode, n_merges);
+	lm_adam *opt;
+	int i;
+	int rc;
+
+	if (!model)
+		return -1;
+	opt = lm_adam_create(model);
+	if (!opt) {
+		lm_free(&model);
+		return -1;
+	}
+	if (*n_io != opt->n) {
+		rc = *n_io == 0 ? 0 : -2;
+		*n_io = opt->n;
+		lm_adam_free(&opt);
+		lm_free(&model);
+		return rc;
+	}
+	for (i = 0; i < opt->n; i++) {
+		*opt->slots[i].param = w[i];
+		opt->slots[i].m = m[i];
+		opt->slots[i].v = v[i];
+	}
+	opt->t = t;
+	rc = lm_save_checkpoint(model, opt, epoch, step, path);
+	lm_adam_free(&opt);
+	lm_free(&model);
+	return rc;
+}
+
+/* lm_load_checkpoint, everything handed back in optimizer order. */
+int ref_ckpt_load_full(const char *path, float *w, float *m, float *v, int n_cap, int *n_out,
+	int *t_out, int *epoch_out, int *step_out, int *vocab_out, int *tied_out)
+{
+	lm *model;
+	lm_adam *opt = NULL;
+	int i;
+
+	model = lm_load_checkpoint(path, &opt, epoch_out, step_out);
+	if (!model || !opt)
+		return -1;
+	*n_out = opt->n;
+	*t_out = opt->t;
+	*vocab_out = model->vocab_size;
+	*tied_out = model->embed->tied;
+	for (i = 0; i < opt->n && i < n_cap; i++) {
+		w[i] = *opt->slots[i].param;
+		m[i] = opt->slots[i].m;
+		v[i] = opt->slots[i].v;
+	}
+	lm_adam_free(&opt);
+	lm_free(&model);
+	return 0;
+}

@@ -49,6 +49,21 @@ def ckpt_moments(n):
     return ((a - 0.5) * 2e-4).astype(np.float32), (b * 3e-6).astype(np.float32)
 
 
+FULL_CKPT_CASES = [(0, 0), (1, 44), (2, 44)]      # (kind, BPE merges): LMCF, LMCV, LMCT
+
+
+def ckpt_weights(n):
+    i = np.arange(n, dtype=np.uint64)
+    a = ((i * np.uint64(2246822519) + np.uint64(7)) % np.uint64(1 << 32)).astype(np.float64) / float(1 << 32)
+    return ((a - 0.5) * 0.08).astype(np.float32)
+
+
+def synthetic_merges(n_merges):
+    """The merge table the reference driver builds: merge i joins tokens 4 + 2i and 4 + 2i + 1 (mod 256)."""
+    i = np.arange(n_merges, dtype=np.int32)
+    return np.stack([4 + (2 * i) % 256, 4 + (2 * i + 1) % 256], axis=1).astype(np.int32)
+
+
 def main():
     ref = RefLib()
     out = {}
@@ -96,6 +111,20 @@ def main():
         json.dump(dict(vocab=vocab, d_model=64, d_ff=256, n_blocks=2, n=n, file_size_full=size,
                        trailer_sha256=digest, trailer_head_hex=tail[:36].hex(), t=1234, epoch=3, step=77, off=off.tolist(), n_per=cnt.tolist(),
                        is_vec=isv.tolist()), f)
+    # whole checkpoints of the three kinds, weights and moments from integer formulas: only hashes
+    import hashlib
+    full = []
+    for mode, n_merges in FULL_CKPT_CASES:
+        nn = ref.full_slot_count(mode, n_merges)
+        w, mm, vv = ckpt_weights(nn), *ckpt_moments(nn)
+        fpath = os.path.join(HERE, f"_full{mode}.bin")
+        ref.ckpt_save_full(fpath, mode, n_merges, w, mm, vv, t=4321, epoch=5, step=66)
+        data = open(fpath, "rb").read()
+        os.remove(fpath)
+        full.append(dict(mode=mode, n_merges=n_merges, n=nn, size=len(data),
+                         sha256=hashlib.sha256(data).hexdigest(), head_hex=data[:40].hex()))
+    with open(os.path.join(HERE, "ckpt_full.json"), "w") as f:
+        json.dump(full, f, indent=0)
     print("golden vectors written:", n, "slots;", len(sched), "schedule points;", len(CASES), "steps")
 
 

@@ -174,6 +174,12 @@ class RefLib:
         L.ref_ckpt_load.restype = C.c_int
         L.ref_ckpt_load.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_int] + \
             [C.POINTER(C.c_int)] * 4
+        L.ref_ckpt_save_full.restype = C.c_int
+        L.ref_ckpt_save_full.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]
+        L.ref_ckpt_load_full.restype = C.c_int
+        L.ref_ckpt_load_full.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int] + \
+            [C.POINTER(C.c_int)] * 6
         L.ref_seg_list.restype = C.c_int
         L.ref_seg_list.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
         self.L = L
@@ -209,6 +215,26 @@ class RefLib:
                                   C.byref(t), C.byref(ep), C.byref(st))
         assert rc == 0, rc
         return dict(n=no.value, t=t.value, epoch=ep.value, step=st.value, m=m, v=v)
+
+    def full_slot_count(self, mode, n_merges):
+        n = C.c_int(0)
+        assert self.L.ref_ckpt_save_full(b"", mode, n_merges, None, None, None, C.byref(n), 0, 0, 0) == 0
+        return n.value
+
+    def ckpt_save_full(self, path, mode, n_merges, w, m, v, *, t, epoch, step):
+        """mode 0: byte-level model (LMCF); 1: BPE embedded (LMCV); 2: BPE + tied embedding (LMCT)."""
+        n = C.c_int(w.size)
+        rc = self.L.ref_ckpt_save_full(path.encode(), mode, n_merges, _ptr(w), _ptr(m), _ptr(v),
+                                       C.byref(n), t, epoch, step)
+        assert rc == 0, rc
+
+    def ckpt_load_full(self, path, n):
+        w, m, v = (np.zeros(n, np.float32) for _ in range(3))
+        out = [C.c_int() for _ in range(6)]
+        rc = self.L.ref_ckpt_load_full(path.encode(), _ptr(w), _ptr(m), _ptr(v), n, *[C.byref(o) for o in out])
+        assert rc == 0, rc
+        no, t, ep, st, vocab, tied = (o.value for o in out)
+        return dict(n=no, t=t, epoch=ep, step=st, vocab=vocab, tied=tied, w=w, m=m, v=v)
 
     def seg_list(self, vocab, cap=512):
         off = np.zeros(cap, np.int32)

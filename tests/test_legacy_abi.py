@@ -380,3 +380,57 @@ def test_optimizer_object_semantics(oracle):
     L.anni_lm_adam_set_offload(0)
     L.anni_lm_adam_free(C.byref(opt))                              # pulls the weights back first
     assert (np.abs(p.astype(np.float64) - rp) <= 2 * np.spacing(np.abs(rp)) + 2e-9).all()
+
+
+def test_resume_from_reference_format_checkpoint_and_save_back(oracle, tmp_path):
+    """A checkpoint in the reference's format (tied-embedding kind, BPE table embedded) is loaded
+    into the optimizer object, two steps run on the GPU, the result is saved in the same format;
+    the saved state equals the oracle stepping from the same file."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from golden.make_golden import ckpt_moments, ckpt_weights, synthetic_merges
+    from anni_b200.engine import lm_param_count
+    L = _mirror()
+    n_merges = 44
+    vocab = 4 + 256 + n_merges
+    k = checkpoint.CkptModel()
+    k.kind, k.tied, k.d_model, k.n_heads, k.d_ff, k.max_ctx, k.n_blocks, k.vocab = 2, 1, 64, 4, 256, 2048, 2, vocab
+    k.n_merges = k.merges_word = n_merges
+    k.n = lm_param_count(64, 256, 2, vocab, True)
+    k.t, k.epoch, k.step = 500, 1, 40
+    w0 = ckpt_weights(k.n)
+    m0, v0 = ckpt_moments(k.n)
+    src = str(tmp_path / "in.ckpt")
+    checkpoint.save_model(src, k, w0, m0, v0, synthetic_merges(n_merges))
+
+    ck = checkpoint.load_model(src)
+    segs = lm_segments(d_model=64, d_ff=256, n_blocks=2, vocab=vocab, tied=True, wd="matrices")
+    assert segs.n == ck["info"].n
+    p, g = ck["w"].copy(), np.zeros(segs.n, np.float32)
+    opt = _make_opt(L, segs, p, g)
+    o = opt.contents
+    assert L.anni_lm_adam_set_moments(opt, ck["m"].ctypes.data, ck["v"].ctypes.data) == 0
+    o.t, o.beta2, o.weight_decay, o.grad_clip = ck["info"].t, 0.95, 0.1, 0.0
+    rng = np.random.default_rng(12)
+    grads = [rng.normal(0, 1e-3, segs.n).astype(np.float32) for _ in range(2)]
+    for gg in grads:
+        g[:] = gg
+        assert L.anni_lm_adam_step_scaled(opt, 3e-4, 0.5) == 0
+    assert L.anni_lm_adam_sync_host(opt) == 0 and o.t == 502
+    info = ck["info"]
+    info.t, info.step = o.t, 42
+    dst = str(tmp_path / "out.ckpt")
+    checkpoint.save_model(dst, info, p, np.ctypeslib.as_array(o.h_m, (segs.n,)),
+                          np.ctypeslib.as_array(o.h_v, (segs.n,)), ck["merges"])
+    L.anni_lm_adam_free(C.byref(opt))
+
+    back = checkpoint.load_model(dst)
+    assert back["info"].t == 502 and back["info"].step == 42 and back["info"].kind == 2
+    rp, rm, rv = w0.copy(), m0.copy(), v0.copy()
+    for i, gg in enumerate(grads):
+        oracle.step(rp, gg.copy(), rm, rv, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=0.0,
+                    grad_scale=0.5, t_before=500 + i, seg_off=segs.offsets, seg_flags=segs.flag_array)
+    # first step's moments are bit-identical; the second starts from masters that may be 1 ulp apart
+    assert f32_ulp_dist(back["m"], rm).max() <= 1 and f32_ulp_dist(back["v"], rv).max() <= 1
+    dp = np.abs(back["w"].astype(np.float64) - rp)
+    assert (dp <= 2 * np.spacing(np.maximum(np.abs(rp), np.abs(w0))) + 2e-6 * np.abs(w0 - rp)).all()
