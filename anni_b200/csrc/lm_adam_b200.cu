@@ -177,6 +177,25 @@ extern "C" void anni_lm_adam_free(anni_lm_adam **popt)
 	opt = *popt;
 	if (opt->d_param)
 		(void)anni_lm_adam_sync_host(opt);	/* weights back to the host before the flats go (lm_adam.c:146-165) */
+	for (int i = 0; i < opt->n_segs; i++) {	/* detach the views: nobody may free a slice of a flat */
+		anni_lm_adam_seg *s = &opt->segs[i];
+
+		if (s->w_mat && s->w_mat->d_data == opt->d_param + s->off) {
+			s->w_mat->d_data = NULL;
+			s->w_mat->on_device = 0;
+		}
+		if (s->dw_mat && opt->d_grad && s->dw_mat->d_data == (float *)opt->d_grad + s->off) {
+			s->dw_mat->d_data = NULL;
+			s->dw_mat->on_device = 0;
+		}
+	}
+	if (opt->snap_stream) {
+		cudaStreamSynchronize((cudaStream_t)opt->snap_stream);
+		cudaEventDestroy((cudaEvent_t)opt->snap_event);
+		cudaStreamDestroy((cudaStream_t)opt->snap_stream);
+		cudaFreeHost(opt->snap_m);
+		cudaFreeHost(opt->snap_v);
+	}
 	release_device(opt);
 	free(opt->h_m);
 	free(opt->h_v);
@@ -325,6 +344,86 @@ static int ensure_device(anni_lm_adam *opt)
 	}
 	if (g_offload_all)
 		opt->offload_mv = 1;
+	return ANNI_OK;
+}
+
+extern "C" int anni_lm_adam_prepare(anni_lm_adam *opt)
+{
+	return opt ? ensure_device(opt) : ANNI_E_ARG;
+}
+
+extern "C" int anni_lm_adam_alias(anni_lm_adam *opt, int tensor, anni_mat *w, anni_mat *dw)
+{
+	anni_lm_adam_seg *s;
+
+	if (!opt || tensor < 0 || tensor >= opt->n_segs || !w || !opt->d_param)
+		return ANNI_E_ARG;
+	s = &opt->segs[tensor];
+	if ((int64_t)w->rows * w->cols != s->n || (dw && (int64_t)dw->rows * dw->cols != s->n))
+		return ANNI_E_ARG;
+	if (dw && opt->grad_dtype != ANNI_DT_F32)
+		return ANNI_E_ARG;	/* a float matrix cannot be a view of a bf16 flat */
+	w->d_data = opt->d_param + s->off;
+	w->on_device = 3;
+	s->w_mat = w;
+	if (dw) {
+		dw->d_data = (float *)opt->d_grad + s->off;
+		dw->on_device = 3;
+		s->dw_mat = dw;
+		s->dw = NULL;	/* gradients of this tensor now arrive on the device */
+	}
+	return ANNI_OK;
+}
+
+extern "C" int anni_lm_adam_snapshot_begin(anni_lm_adam *opt)
+{
+	const size_t nb = opt ? (size_t)opt->n * elem_size(opt->state_dtype) : 0;
+	cudaStream_t st;
+	cudaEvent_t ev;
+
+	if (!opt || !opt->d_m || !opt->d_v)
+		return ANNI_E_ARG;
+	if (!opt->snap_stream) {
+		if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess
+		    || cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess
+		    || cudaMallocHost(&opt->snap_m, nb) != cudaSuccess
+		    || cudaMallocHost(&opt->snap_v, nb) != cudaSuccess) {
+			(void)cudaGetLastError();
+			return ANNI_E_NOMEM;
+		}
+		opt->snap_stream = st;
+		opt->snap_event = ev;
+	}
+	st = (cudaStream_t)opt->snap_stream;
+	ev = (cudaEvent_t)opt->snap_event;
+	/* the copies start once everything queued so far on the step stream (the legacy stream) is done */
+	if (cudaEventRecord(ev, 0) != cudaSuccess || cudaStreamWaitEvent(st, ev, 0) != cudaSuccess
+	    || cudaMemcpyAsync(opt->snap_m, opt->d_m, nb, cudaMemcpyDeviceToHost, st) != cudaSuccess
+	    || cudaMemcpyAsync(opt->snap_v, opt->d_v, nb, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+		return ANNI_E_CUDA;
+	return ANNI_OK;
+}
+
+extern "C" int anni_lm_adam_snapshot_finish(anni_lm_adam *opt)
+{
+	int64_t i;
+
+	if (!opt || !opt->snap_stream)
+		return ANNI_E_ARG;
+	if (cudaStreamSynchronize((cudaStream_t)opt->snap_stream) != cudaSuccess)
+		return ANNI_E_CUDA;
+	if (opt->state_dtype == ANNI_DT_F32) {
+		memcpy(opt->h_m, opt->snap_m, (size_t)opt->n * 4u);
+		memcpy(opt->h_v, opt->snap_v, (size_t)opt->n * 4u);
+	} else {
+		const uint16_t *pm = (const uint16_t *)opt->snap_m;
+		const uint16_t *pv = (const uint16_t *)opt->snap_v;
+
+		for (i = 0; i < opt->n; i++) {
+			opt->h_m[i] = bf16_to_f32_host(pm[i]);
+			opt->h_v[i] = bf16_to_f32_host(pv[i]);
+		}
+	}
 	return ANNI_OK;
 }
 

@@ -47,6 +47,8 @@ typedef struct anni_lm_adam_seg {
 	int64_t		off;
 	int64_t		n;
 	uint32_t	flags;
+	anni_mat	*w_mat;	/* trainer matrices whose device twins are views into the flats, or NULL */
+	anni_mat	*dw_mat;
 } anni_lm_adam_seg;
 
 /* Mirrors lm_adam (lang/lm_adam.h:31-54); same names where the field exists there. */
@@ -79,6 +81,10 @@ typedef struct anni_lm_adam {
 	int		last_error;	/* ANNI_E_* of the last step, 0 if it ran */
 	double		loss_scale;	/* > 0: gradients arrive multiplied by this; folded into grad_scale */
 	int		exact_update;	/* 1: ANNI_STEP_EXACT_UPDATE (default with fp32 moments) */
+	void		*snap_m;	/* pinned staging and side stream of an in-flight snapshot */
+	void		*snap_v;
+	void		*snap_stream;
+	void		*snap_event;
 	anni_optstep	*engine;
 } anni_lm_adam;
 
@@ -101,6 +107,27 @@ int	anni_lm_adam_sync_host(anni_lm_adam *opt);
 void	anni_lm_adam_set_offload(int on);
 /* Upload the host gradient arrays (tensors with dw != NULL) into the device flat: seg_gather's job. */
 int	anni_lm_adam_upload_grads(anni_lm_adam *opt);
+/*
+** Hand-off with the forward / backward pass, as the reference does it (lang/lm_adam.c:239-282):
+** the device twin of a weight matrix and of its gradient become VIEWS into the optimizer's
+** flats (d_data = d_param + off resp. d_grad + off, on_device = aliased), so the backward GEMMs
+** accumulate dW straight into the gradient flat and the step updates the weights in place -- no
+** gather, no scatter.  prepare allocates the flats and uploads the weights ahead of the first
+** step (gpu_buffers_init); alias attaches one tensor (gradients must be fp32 to alias dw; pass
+** dw = NULL otherwise); free pulls the weights back to the host arrays and detaches every view
+** (unalias_segs, lang/lm_adam.c:146-165), so the trainer never frees a slice of a flat.
+*/
+int	anni_lm_adam_prepare(anni_lm_adam *opt);
+int	anni_lm_adam_alias(anni_lm_adam *opt, int tensor, anni_mat *w, anni_mat *dw);
+/*
+** Snapshot of m and v for a checkpoint without stalling the step stream (the reference's offload
+** copies synchronously, lang/lm_adam.c:314-334): begin queues device-to-host copies into pinned
+** staging on a side stream that first waits for the work queued so far; finish waits for them
+** and converts into h_m / h_v (fp32, arena order).  Steps may be queued between the two calls
+** only if they do not touch m / v before finish -- i.e. overlap it with the next forward/backward.
+*/
+int	anni_lm_adam_snapshot_begin(anni_lm_adam *opt);
+int	anni_lm_adam_snapshot_finish(anni_lm_adam *opt);
 /* Load m/v (fp32, arena order) e.g. from a checkpoint; uploaded at the next step. */
 int	anni_lm_adam_set_moments(anni_lm_adam *opt, const float *m, const float *v);
 

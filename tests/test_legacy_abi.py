@@ -229,7 +229,7 @@ class Tensor(C.Structure):
 
 class Seg(C.Structure):
     _fields_ = [("w", C.c_void_p), ("dw", C.c_void_p), ("off", C.c_int64), ("n", C.c_int64),
-                ("flags", C.c_uint32)]
+                ("flags", C.c_uint32), ("w_mat", C.c_void_p), ("dw_mat", C.c_void_p)]
 
 
 class LmAdam(C.Structure):
@@ -241,7 +241,8 @@ class LmAdam(C.Structure):
                 ("offload_mv", C.c_int), ("weight_decay", d), ("grad_clip", d), ("last_grad_norm", d),
                 ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("last_skipped", C.c_int),
                 ("last_error", C.c_int), ("loss_scale", d), ("exact_update", C.c_int),
-                ("engine", C.c_void_p)]
+                ("snap_m", C.c_void_p), ("snap_v", C.c_void_p), ("snap_stream", C.c_void_p),
+                ("snap_event", C.c_void_p), ("engine", C.c_void_p)]
 
 
 def _mirror():
@@ -434,3 +435,67 @@ def test_resume_from_reference_format_checkpoint_and_save_back(oracle, tmp_path)
     assert f32_ulp_dist(back["m"], rm).max() <= 1 and f32_ulp_dist(back["v"], rv).max() <= 1
     dp = np.abs(back["w"].astype(np.float64) - rp)
     assert (dp <= 2 * np.spacing(np.maximum(np.abs(rp), np.abs(w0))) + 2e-6 * np.abs(w0 - rp)).all()
+
+
+def test_aliased_matrices_and_async_moment_snapshot(oracle):
+    """Hand-off as the reference does it: weight / gradient matrices become views into the
+    optimizer's flats (gradients written on the device, weights updated in place), vectors stay
+    host-resident; m / v are snapshotted on a side stream; free pulls the weights back and
+    detaches the views."""
+    class Mat(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("d_data", C.c_void_p), ("rows", C.c_int),
+                    ("cols", C.c_int), ("on_device", C.c_int)]
+    L = _mirror()
+    Lg = _legacy()
+    Lg.gpu_memcpy_h2d.restype = C.c_int
+    Lg.gpu_memcpy_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    for f in (L.anni_lm_adam_prepare, L.anni_lm_adam_snapshot_begin, L.anni_lm_adam_snapshot_finish):
+        f.restype = C.c_int
+        f.argtypes = [C.POINTER(LmAdam)]
+    L.anni_lm_adam_alias.restype = C.c_int
+    L.anni_lm_adam_alias.argtypes = [C.POINTER(LmAdam), C.c_int, C.POINTER(Mat), C.POINTER(Mat)]
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n, off = segs.n, segs.offsets
+    p, g0, _, _ = make_inputs(n, seed=71)
+    g = np.zeros(n, np.float32)
+    opt = _make_opt(L, segs, p, g)
+    o = opt.contents
+    o.beta2, o.weight_decay, o.grad_clip = 0.95, 0.1, 1.0
+    assert L.anni_lm_adam_prepare(opt) == 0 and o.d_param and o.params_valid == 1
+    mats = {}
+    for i in range(len(segs)):
+        if not (segs.flags[i] & 1):                                  # vectors stay host-resident
+            continue
+        rows = 64
+        w = Mat(p[off[i]:].ctypes.data, None, rows, segs.sizes[i] // rows, 0)
+        dw = Mat(g[off[i]:].ctypes.data, None, rows, segs.sizes[i] // rows, 0)
+        assert L.anni_lm_adam_alias(opt, i, C.byref(w), C.byref(dw)) == 0
+        assert w.d_data == o.d_param + 4 * off[i] and dw.d_data == o.d_grad + 4 * off[i]
+        assert w.on_device == 3 and dw.on_device == 3
+        mats[i] = (w, dw)
+    assert len(mats) == 14
+    rp, rm, rv = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    for step in range(2):
+        for i in range(len(segs)):
+            sl = slice(int(off[i]), int(off[i + 1]))
+            if i in mats:                                            # "backward GEMM": dW on the device
+                chunk = np.ascontiguousarray(g0[sl] * (step + 1))
+                assert Lg.gpu_memcpy_h2d(mats[i][1].d_data, chunk.ctypes.data, chunk.nbytes) == 0
+                Lg.gpu_device_sync()
+            else:                                                    # bias / LN gradients on the host
+                g[sl] = g0[sl] * (step + 1)
+        assert L.anni_lm_adam_step_scaled(opt, 1e-3, 1.0) == 0
+        gg = g0 * np.float32(step + 1)
+        info = oracle.step(rp, gg, rm, rv, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                           t_before=step, check_finite=True, seg_off=off, seg_flags=segs.flag_array)
+        assert abs(o.last_grad_norm - info["norm"]) <= 1e-9 * info["norm"]
+    assert L.anni_lm_adam_snapshot_begin(opt) == 0                  # copies run beside whatever comes next
+    assert L.anni_lm_adam_snapshot_finish(opt) == 0
+    hm = np.ctypeslib.as_array(o.h_m, (n,)).copy()
+    hv = np.ctypeslib.as_array(o.h_v, (n,)).copy()
+    assert f32_ulp_dist(hm, rm).max() <= 1 and f32_ulp_dist(hv, rv).max() <= 1
+    L.anni_lm_adam_free(C.byref(opt))
+    for w, dw in mats.values():                                      # views detached, weights on the host
+        assert not w.d_data and not dw.d_data and w.on_device == 0 and dw.on_device == 0
+    dp = np.abs(p.astype(np.float64) - rp)
+    assert (dp <= 2 * np.spacing(np.abs(rp)) + 4e-9).all()
