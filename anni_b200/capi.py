@@ -34,6 +34,11 @@ class Hyper(C.Structure):
                 ("grad_scale", C.c_double), ("t", C.c_int), ("flags", C.c_int)]
 
 
+class SegDerived(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("pack_off", C.c_int64),
+                ("pack_ld", C.c_int32), ("reserved", C.c_int32), ("fp8_t_off", C.c_int64)]
+
+
 class Status(C.Structure):
     _fields_ = [("sumsq", C.c_double), ("norm", C.c_double), ("eff_scale", C.c_double),
                 ("loss_scale", C.c_double), ("skipped", C.c_int32), ("error", C.c_int32),
@@ -62,6 +67,8 @@ def lib():
         f = getattr(L, name)
         f.restype = i
         f.argtypes = [vp, C.POINTER(Hyper), vp]
+    L.anni_optstep_set_derived.restype = i
+    L.anni_optstep_set_derived.argtypes = [vp, vp, vp, vp]
     L.anni_optstep_set_peers.restype = i
     L.anni_optstep_set_peers.argtypes = [vp, vp, vp, vp, i, C.c_uint64]
     L.anni_optstep_reduce_norm.restype = i

@@ -531,7 +531,8 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 
 template <typename GradT, typename StateT, bool EXACT>
 __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t e, double coef,
-	uint32_t sflags, float &tmax)
+	uint32_t sflags, float &tmax, uint64_t seg_base, int64_t pack_off, uint32_t pack_ld,
+	uint32_t pack_cols)
 {
 	const float lrwd = (sflags & ANNI_SEG_WD) ? a.lrwd : 0.0f;
 	f32x4 g = io4<GradT>::load(a.grad, e);
@@ -557,6 +558,15 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 #pragma unroll
 		for (int k = 0; k < ANNI_UVEC; k++)
 			tmax = fmaxf(tmax, fabsf(p.x[k]));
+	}
+	if (pack_ld != 0) {
+		/* the same twin once more, as a block of the layer's packed [Wq|Wk|Wv] matrix;
+		** four consecutive elements stay inside one row because cols % 4 == 0 (checked on the host) */
+		const uint32_t ws = (uint32_t)(e - seg_base);
+		const uint32_t r = ws / pack_cols;
+
+		io4<__nv_bfloat16>::store(a.qkv_packed, (uint64_t)pack_off + (uint64_t)r * pack_ld
+		    + (ws - r * pack_cols), p);
 	}
 	if (a.flags & ANNI_STEP_ZERO_GRAD)
 		io4<GradT>::zero(a.grad, e);
@@ -594,6 +604,14 @@ __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64
 			if (sflags & ANNI_SEG_TWIN_FP8)
 				atomicMax(reinterpret_cast<int *>(&a.seg_amax[s]),
 				    __float_as_int(fabsf(p)));
+			if (a.seg_aux && a.seg_aux[s].pack_ld != 0) {
+				const anni_seg_derived ax = a.seg_aux[s];
+				const uint32_t ws = (uint32_t)((int64_t)(a.arena_off + i) - a.seg_off[s]);
+				const uint32_t r = ws / (uint32_t)ax.cols;
+
+				io8<__nv_bfloat16>::store1(a.qkv_packed, (uint64_t)ax.pack_off
+				    + (uint64_t)r * (uint32_t)ax.pack_ld + (ws - r * (uint32_t)ax.cols), p);
+			}
 		}
 		if (a.flags & ANNI_STEP_ZERO_GRAD)
 			io8<GradT>::store1(a.grad, i, 0.0f);
@@ -646,7 +664,14 @@ __device__ __forceinline__ void update_phase(const anni_launch &a, const decisio
 					amax_flush(a, amax_seg, tmax);
 				amax_seg = (sflags & ANNI_SEG_TWIN_FP8) ? seg : -1;
 			}
-			update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax);
+			if (a.seg_aux) {
+				const anni_seg_derived ax = a.seg_aux[seg];
+
+				update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax,
+				    (uint64_t)a.seg_off[seg] - a.arena_off, ax.pack_off, (uint32_t)ax.pack_ld,
+				    (uint32_t)ax.cols);
+			} else
+				update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax, 0, 0, 0, 1);
 		} else if (whole) {
 			io4<GradT>::zero(a.grad, base + t4);	/* skipped step: only the gradients change */
 		} else
@@ -693,7 +718,7 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a)
 		while (abase >= a.seg_off[seg + 1])
 			seg++;
 		if (a.aligned && base + ANNI_UCHUNK <= a.n && abase + ANNI_UCHUNK <= a.seg_off[seg + 1]) {
-			if (a.seg_flags[seg] & ANNI_SEG_TWIN_FP8) {
+			if ((a.seg_flags[seg] & ANNI_SEG_TWIN_FP8) && !(a.seg_aux && a.seg_aux[seg].fp8_t_off >= 0)) {
 				const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[seg]));
 				const uint64_t e = base + t4;
 				f32x4 p = io4<float>::load(a.master, e);
@@ -716,7 +741,7 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a)
 					break;
 				const int s = seg_find(a.seg_off, a.n_seg, (int64_t)(a.arena_off + i));
 
-				if (a.seg_flags[s] & ANNI_SEG_TWIN_FP8) {
+				if ((a.seg_flags[s] & ANNI_SEG_TWIN_FP8) && !(a.seg_aux && a.seg_aux[s].fp8_t_off >= 0)) {
 					const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[s]));
 
 					const uint8_t q8 = (uint8_t)__nv_cvt_float_to_fp8(a.master[i] * inv,
@@ -1038,6 +1063,55 @@ __global__ void __launch_bounds__(ANNI_THREADS) barrier_timeout_kernel(anni_cont
 		atomicExch(&ctl->error, ANNI_E_ARG);	/* the barrier must not have opened */
 }
 
+/*
+** e4m3 twins in the transposed [cols][rows] layout the forward GEMM wants
+** (the reference's f32_transpose_to_fp8_kernel, one launch per tensor): here
+** one launch for every such tensor.  64x64 tiles, dealt round-robin over a
+** persistent grid; tile_prefix[s] = number of tiles before tensor s.  A tile is
+** read row-wise (256-byte rows of the fp32 master), quantised with the
+** tensor's scale, turned in shared memory and written column-wise as 64-byte rows.
+*/
+#define ANNI_TT	64
+
+__global__ void __launch_bounds__(ANNI_THREADS) quantize_transposed_kernel(const anni_launch a,
+	const int64_t *tile_prefix, int64_t n_tiles)
+{
+	__shared__ uint8_t tile[ANNI_TT][ANNI_TT + 4];
+	const int tx = threadIdx.x & 63;	/* column inside the tile when reading */
+	const int ty = threadIdx.x >> 6;	/* 4 rows per pass */
+	int seg = 0;
+
+	if (a.ctl->skipped)
+		return;
+	if (blockIdx.x == 0)
+		for (int s = threadIdx.x; s < a.n_seg; s += blockDim.x)
+			if ((a.seg_flags[s] & ANNI_SEG_TWIN_FP8) && a.seg_aux[s].fp8_t_off >= 0)
+				a.seg_scale[s] = fp8_scale(a.seg_amax[s]);
+	for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+		while (seg + 1 < a.n_seg && tile_prefix[seg + 1] <= t)
+			seg++;
+		const anni_seg_derived ax = a.seg_aux[seg];
+		const int tiles_x = (ax.cols + ANNI_TT - 1) / ANNI_TT;
+		const int64_t lt = t - tile_prefix[seg];
+		const int r0 = (int)(lt / tiles_x) * ANNI_TT;
+		const int c0 = (int)(lt % tiles_x) * ANNI_TT;
+		const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[seg]));
+		const float *src = a.master + ((uint64_t)a.seg_off[seg] - a.arena_off);
+		uint8_t *dst = a.fp8_t + ax.fp8_t_off;
+
+		for (int j = ty; j < ANNI_TT; j += ANNI_THREADS / 64)
+			if (r0 + j < ax.rows && c0 + tx < ax.cols)
+				tile[j][tx] = (uint8_t)__nv_cvt_float_to_fp8(
+				    src[(uint64_t)(r0 + j) * ax.cols + c0 + tx] * inv, __NV_SATFINITE, __NV_E4M3);
+		__syncthreads();
+		/* now tx walks the rows of the source (contiguous in the transposed destination) */
+		for (int j = ty; j < ANNI_TT; j += ANNI_THREADS / 64)
+			if (c0 + j < ax.cols && r0 + tx < ax.rows)
+				dst[(uint64_t)(c0 + j) * ax.rows + r0 + tx] = tile[tx][j];
+		__syncthreads();
+	}
+}
+
 /* One-shot fp32 -> bf16 of a flat buffer (seeding the twin; num/gpu.h:73 of the reference). */
 __global__ void __launch_bounds__(ANNI_THREADS) f32_to_bf16_kernel(uint16_t *dst, const float *src,
 	uint64_t n, int aligned)
@@ -1238,6 +1312,18 @@ extern "C" int anni_launch_fused(const anni_launch *a, int grad_dtype, int state
 	if (sb)
 		return launch_fused_t<float, __nv_bfloat16>(a, blocks, st);
 	return launch_fused_t<float, float>(a, blocks, st);
+}
+
+extern "C" int anni_launch_quantize_transposed(const anni_launch *a, const int64_t *tile_prefix,
+	int64_t n_tiles, int blocks, cudaStream_t st)
+{
+	if (!a || !tile_prefix || !a->seg_aux || !a->fp8_t || blocks < 1)
+		return ANNI_E_ARG;
+	if (n_tiles <= 0)
+		return ANNI_OK;
+	quantize_transposed_kernel<<<blocks, ANNI_THREADS, 0, st>>>(*a, tile_prefix, n_tiles);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
 
 extern "C" int anni_launch_barrier_timeout(anni_control *ctl, int blocks, unsigned max_polls, cudaStream_t st)

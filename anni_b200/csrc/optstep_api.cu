@@ -18,6 +18,11 @@ struct anni_optstep {
 	uint32_t		*d_seg_flags;
 	float			*d_amax;
 	float			*d_scale;
+	anni_seg_derived	*d_aux;		/* derived-twin table (anni_optstep_set_derived) */
+	int64_t			*d_tile_prefix;	/* tiles before each tensor, transposed e4m3 twins */
+	int64_t			n_tiles;
+	int64_t			*h_seg_off;	/* host copies, for argument checks */
+	uint32_t		*h_seg_flags;
 	int			n_seg;
 	int			has_fp8;
 	int			bound;
@@ -25,6 +30,8 @@ struct anni_optstep {
 	int			blocks_coop;
 	int			blocks_split;
 };
+
+static int derived_after_step(anni_optstep *h, const anni_launch *la, cudaStream_t st);
 
 /* ANNI_B200_SUPERCHUNK=k: 2^k consecutive chunks per block per round (tuning knob). */
 static int superchunk_log2(void)
@@ -96,6 +103,14 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 	for (i = 0; i < h->n_seg; i++)
 		if (flg[i] & ANNI_SEG_TWIN_FP8)
 			h->has_fp8 = 1;
+	h->h_seg_off = (int64_t *)malloc((size_t)(h->n_seg + 1) * sizeof(int64_t));
+	h->h_seg_flags = (uint32_t *)malloc((size_t)h->n_seg * sizeof(uint32_t));
+	if (!h->h_seg_off || !h->h_seg_flags) {
+		anni_optstep_destroy(h);
+		return ANNI_E_NOMEM;
+	}
+	memcpy(h->h_seg_off, off, (size_t)(h->n_seg + 1) * sizeof(int64_t));
+	memcpy(h->h_seg_flags, flg, (size_t)h->n_seg * sizeof(uint32_t));
 	if (cudaMalloc((void **)&h->ctl, sizeof(anni_control)) != cudaSuccess
 	    || cudaMalloc((void **)&h->d_seg_off, (size_t)(h->n_seg + 1) * sizeof(int64_t)) != cudaSuccess
 	    || cudaMalloc((void **)&h->d_seg_flags, (size_t)h->n_seg * sizeof(uint32_t)) != cudaSuccess
@@ -153,6 +168,10 @@ extern "C" void anni_optstep_destroy(anni_optstep *h)
 	cudaFree(h->d_seg_flags);
 	cudaFree(h->d_amax);
 	cudaFree(h->d_scale);
+	cudaFree(h->d_aux);
+	cudaFree(h->d_tile_prefix);
+	free(h->h_seg_off);
+	free(h->h_seg_flags);
 	free(h);
 }
 
@@ -202,7 +221,8 @@ extern "C" int anni_optstep_step(anni_optstep *h, const anni_optstep_hyper *hp, 
 	if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
 	    != cudaSuccess)
 		return ANNI_E_CUDA;
-	return anni_launch_fused(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_coop, st);
+	rc = anni_launch_fused(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_coop, st);
+	return rc != ANNI_OK ? rc : derived_after_step(h, &la, st);
 }
 
 extern "C" int anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
@@ -227,6 +247,85 @@ extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp
 	    != cudaSuccess)
 		return ANNI_E_CUDA;
 	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+}
+
+extern "C" int anni_optstep_set_derived(anni_optstep *h, const anni_seg_derived *aux, void *qkv_packed,
+	void *fp8_t)
+{
+	int64_t *prefix;
+	int64_t tiles = 0;
+	int any_pack = 0;
+	int any_t = 0;
+	int i;
+
+	if (!h)
+		return ANNI_E_ARG;
+	cudaFree(h->d_aux);
+	cudaFree(h->d_tile_prefix);
+	h->d_aux = NULL;
+	h->d_tile_prefix = NULL;
+	h->n_tiles = 0;
+	h->la.seg_aux = NULL;
+	h->la.qkv_packed = NULL;
+	h->la.fp8_t = NULL;
+	if (!aux)
+		return ANNI_OK;
+	if (h->cfg.shard_off != 0 || h->cfg.shard_n != h->cfg.n_arena)
+		return ANNI_E_ARG;	/* whole-arena engines only */
+	prefix = (int64_t *)malloc((size_t)(h->n_seg + 1) * sizeof(int64_t));
+	if (!prefix)
+		return ANNI_E_NOMEM;
+	for (i = 0; i < h->n_seg; i++) {
+		const int64_t n = h->h_seg_off[i + 1] - h->h_seg_off[i];
+		const int shaped = aux[i].rows > 0 && aux[i].cols > 0;
+
+		prefix[i] = tiles;
+		if (shaped && (int64_t)aux[i].rows * aux[i].cols != n)
+			goto bad;
+		if (aux[i].pack_ld != 0) {
+			/* vector stores of four elements must stay inside one row, 8-byte aligned */
+			if (!shaped || !(h->h_seg_flags[i] & ANNI_SEG_TWIN_BF16) || aux[i].cols % 4 != 0
+			    || aux[i].pack_ld % 4 != 0 || aux[i].pack_off % 4 != 0 || aux[i].pack_off < 0
+			    || aux[i].pack_ld < aux[i].cols)
+				goto bad;
+			any_pack = 1;
+		}
+		if (aux[i].fp8_t_off >= 0) {
+			if (!shaped || !(h->h_seg_flags[i] & ANNI_SEG_TWIN_FP8))
+				goto bad;
+			tiles += (int64_t)((aux[i].rows + 63) / 64) * ((aux[i].cols + 63) / 64);
+			any_t = 1;
+		}
+	}
+	prefix[h->n_seg] = tiles;
+	if ((any_pack && !qkv_packed) || (any_t && !fp8_t))
+		goto bad;
+	if (cudaMalloc((void **)&h->d_aux, (size_t)h->n_seg * sizeof(anni_seg_derived)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_tile_prefix, (size_t)(h->n_seg + 1) * sizeof(int64_t)) != cudaSuccess
+	    || cudaMemcpy(h->d_aux, aux, (size_t)h->n_seg * sizeof(anni_seg_derived),
+	    cudaMemcpyHostToDevice) != cudaSuccess
+	    || cudaMemcpy(h->d_tile_prefix, prefix, (size_t)(h->n_seg + 1) * sizeof(int64_t),
+	    cudaMemcpyHostToDevice) != cudaSuccess) {
+		free(prefix);
+		return ANNI_E_CUDA;
+	}
+	free(prefix);
+	h->n_tiles = tiles;
+	h->la.seg_aux = h->d_aux;
+	h->la.qkv_packed = (uint16_t *)qkv_packed;
+	h->la.fp8_t = (uint8_t *)fp8_t;
+	return ANNI_OK;
+bad:
+	free(prefix);
+	return ANNI_E_ARG;
+}
+
+/* the transposed e4m3 twins: one more launch after the step's own quantise phase */
+static int derived_after_step(anni_optstep *h, const anni_launch *la, cudaStream_t st)
+{
+	if (h->n_tiles <= 0)
+		return ANNI_OK;
+	return anni_launch_quantize_transposed(la, h->d_tile_prefix, h->n_tiles, h->blocks_split, st);
 }
 
 extern "C" int anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad,
@@ -274,6 +373,7 @@ extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hype
 extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
 {
 	anni_launch la;
+	int rc;
 
 	if (!h || !h->bound)
 		return ANNI_E_ARG;
@@ -281,7 +381,8 @@ extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
 		return ANNI_OK;
 	la = h->la;
 	la.flags = ANNI_LAUNCH_HAS_FP8;
-	return anni_launch_quantize(&la, h->blocks_split, (cudaStream_t)stream);
+	rc = anni_launch_quantize(&la, h->blocks_split, (cudaStream_t)stream);
+	return rc != ANNI_OK ? rc : derived_after_step(h, &la, (cudaStream_t)stream);
 }
 
 extern "C" int anni_optstep_selftest_barrier_timeout(anni_optstep *h, unsigned max_polls, void *stream)

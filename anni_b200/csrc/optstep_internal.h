@@ -66,6 +66,9 @@ typedef struct anni_launch {
 	const uint32_t	*seg_flags;	/* device, n_seg */
 	float		*seg_amax;	/* device, n_seg */
 	float		*seg_scale;	/* device, n_seg */
+	const anni_seg_derived *seg_aux;	/* device, n_seg, or NULL: shapes and targets of the derived twins */
+	uint16_t	*qkv_packed;	/* [Wq|Wk|Wv] bf16 matrices, one per layer */
+	uint8_t		*fp8_t;		/* transposed e4m3 twins */
 	int		n_seg;
 	int		flags;		/* ANNI_STEP_* | ANNI_LAUNCH_* */
 	int		aligned;	/* every buffer 16-byte aligned: vector path allowed */
@@ -114,6 +117,8 @@ int	anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, in
 int	anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
 		cudaStream_t st);
 int	anni_launch_quantize(const anni_launch *a, int blocks, cudaStream_t st);
+int	anni_launch_quantize_transposed(const anni_launch *a, const int64_t *tile_prefix, int64_t n_tiles,
+		int blocks, cudaStream_t st);
 int	anni_launch_barrier_timeout(anni_control *ctl, int blocks, unsigned max_polls, cudaStream_t st);
 int	anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
 int	anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st);

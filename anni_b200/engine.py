@@ -107,6 +107,30 @@ def lm_segments(d_model, d_ff, n_blocks, vocab, tied, *, wd="matrices", twin="bf
     return s
 
 
+def lm_derived(segs, d_model, d_ff, *, pack_qkv=True, fp8_transposed=True):
+    """Derived-twin table of an LM segment list: per layer one packed [Wq|Wk|Wv] (D x 3D) bf16
+    matrix, and the e4m3 twins of the block matrices in the transposed [cols][rows] layout.
+    Returns (aux list, elements of the packed buffer, bytes of the transposed buffer)."""
+    D, FF = d_model, d_ff
+    shapes = {"wq": (D, D), "wk": (D, D), "wv": (D, D), "wo": (D, D), "w1": (D, FF), "w2": (FF, D)}
+    aux, packed, t_bytes = [], 0, 0
+    for name, n, flags in zip(segs.names, segs.sizes, segs.flags):
+        a = capi.SegDerived(0, 0, 0, 0, 0, -1)
+        kind = name.split(".")[-1]
+        if name.startswith("blk") and kind in shapes:
+            a.rows, a.cols = shapes[kind]
+            if pack_qkv and kind in ("wq", "wk", "wv") and (flags & SEG_TWIN_BF16):
+                layer = int(name[3:name.index(".")])
+                a.pack_ld = 3 * D
+                a.pack_off = layer * 3 * D * D + ("wq", "wk", "wv").index(kind) * D
+                packed = max(packed, (layer + 1) * 3 * D * D)
+            if fp8_transposed and (flags & SEG_TWIN_FP8):
+                a.fp8_t_off = t_bytes
+                t_bytes += n
+        aux.append(a)
+    return aux, packed, t_bytes
+
+
 # the benchmark configurations' shapes (element counts follow lm_param_count, lang/lm_adam.c:59-77)
 LM_SHAPES = {
     "talk170m": dict(d_model=1024, d_ff=4096, n_blocks=12, vocab=16384, tied=False),   # 184,676,352
@@ -225,6 +249,17 @@ class OptStep:
 
     def update(self, hp, stream=None):
         check("anni_optstep_update", self.L.anni_optstep_update(self.h, C.byref(hp), self._stream(stream)))
+
+    def set_derived(self, aux, qkv_packed=None, fp8_t=None):
+        """Derived twins emitted by the step: ``aux`` is a list of capi.SegDerived (one per tensor),
+        ``qkv_packed`` a bf16 tensor for the packed [Wq|Wk|Wv] matrices, ``fp8_t`` a uint8 tensor
+        for the transposed e4m3 twins (see anni_optstep_set_derived)."""
+        arr = (capi.SegDerived * len(aux))(*aux) if aux else None
+        self._derived = (arr, qkv_packed, fp8_t)        # keep the buffers alive
+        check("anni_optstep_set_derived",
+              self.L.anni_optstep_set_derived(self.h, arr,
+                                              qkv_packed.data_ptr() if qkv_packed is not None else None,
+                                              fp8_t.data_ptr() if fp8_t is not None else None))
 
     def set_peers(self, peer_grad, peer_twin, peer_twin_fp8, arena_off_padded):
         """Peer-accessible device pointers (ints) of every rank's full gradient / twin arenas."""

@@ -165,6 +165,33 @@ float	*anni_optstep_amax_buffer(anni_optstep *h);	/* device float[n_seg] */
 float	*anni_optstep_scale_buffer(anni_optstep *h);	/* device float[n_seg]: dequantisation scales */
 
 /*
+** Derived twins the forward pass consumes, emitted by the step instead of being rebuilt from
+** the twins afterwards (in the reference: qkv_wt_pack_kernel, num/gpu_cuda.cu:6456, once per
+** optimizer step and layer; f32_transpose_to_fp8_kernel, :898-924, the [N,K] layout of e4m3
+** weights).  One entry per tensor of the segment table:
+**   rows, cols     the matrix shape (rows * cols = tensor elements); 0, 0 for vectors
+**   pack_ld        != 0: the tensor's bf16 twin is ALSO stored into `qkv_packed` as a block of a
+**                  wider row-major matrix: element (r, c) at pack_off + r * pack_ld + c.  For a
+**                  layer's [Wq|Wk|Wv] (D x 3D): pack_ld = 3D, pack_off = layer base + 0 / D / 2D.
+**   fp8_t_off      >= 0 (tensor must carry ANNI_SEG_TWIN_FP8): its e4m3 twin is written
+**                  TRANSPOSED ([cols][rows], same per-tensor scale) at this byte offset of
+**                  `fp8_t` instead of row-major into twin_fp8.  -1: row-major as usual.
+** Arrays are host memory and are copied; buffers are device memory owned by the caller.
+** Single-GPU engines only (shard = whole arena).
+*/
+typedef struct anni_seg_derived {
+	int32_t	rows;
+	int32_t	cols;
+	int64_t	pack_off;
+	int32_t	pack_ld;
+	int32_t	reserved;
+	int64_t	fp8_t_off;
+} anni_seg_derived;
+
+int	anni_optstep_set_derived(anni_optstep *h, const anni_seg_derived *aux, void *qkv_packed,
+		void *fp8_t);
+
+/*
 ** ZeRO-1 over peer memory (NVLink / NVSwitch), no counterpart in the reference
 ** (it is single-GPU).  Instead of an NCCL reduce-scatter before and an
 ** all-gather after the step, the kernels themselves move the data:

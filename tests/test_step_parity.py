@@ -173,3 +173,57 @@ def test_bounded_wait_runs_out_and_engine_recovers(oracle):
     out = dict(p=to_host(eng.master), m=to_host(eng.m), v=to_host(eng.v))
     check_step(out, rp, rm, rv, p, exact_moments=not info["norm"] > 1.0)
     eng.close()
+
+
+@pytest.mark.parametrize("split", [False, True])
+def test_derived_twins_packed_qkv_and_transposed_fp8(oracle, split):
+    """Twin consumers fed by the step itself: per layer the packed [Wq|Wk|Wv] bf16 matrix (here the
+    attention matrices keep bf16 twins), and e4m3 twins of the FFN / output matrices in the
+    transposed [cols][rows] layout -- both equal to what the reference's separate kernels would
+    build from the GPU master (num/gpu_cuda.cu:6456, :898-924)."""
+    import torch
+    from anni_b200.capi import SEG_TWIN_BF16, SEG_TWIN_FP8, SEG_WD
+    from anni_b200.engine import OptStep, lm_derived
+    from parity_util import to_dev, to_host
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin="fp8")
+    for i, name in enumerate(segs.names):                       # attention inputs stay bf16 for the packed matrix
+        if name.endswith((".wq", ".wk", ".wv")):
+            segs.flags[i] = SEG_WD | SEG_TWIN_BF16
+    D, FF, n = 64, 256, segs.n
+    p, g, m, v = make_inputs(n, seed=13, grad_dtype=DT_BF16)
+    eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_F32).allocate()
+    for t_, a_ in ((eng.master, p), (eng.grad, g), (eng.m, m), (eng.v, v)):
+        t_.copy_(to_dev(a_))
+    aux, n_packed, t_bytes = lm_derived(segs, D, FF)
+    assert n_packed == 2 * 3 * D * D and t_bytes == 2 * (D * D + 2 * D * FF)
+    packed = torch.zeros(n_packed, dtype=torch.bfloat16, device="cuda")
+    fp8_t = torch.zeros(t_bytes, dtype=torch.uint8, device="cuda")
+    eng.set_derived(aux, packed, fp8_t)
+    hp = OptStep.hyper(**dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t=50))
+    (eng.step_split if split else eng.step)(hp)
+    assert eng.status().error == 0
+    gp, t16, t8 = to_host(eng.master), to_host(eng.twin_bf16), to_host(eng.twin_fp8)
+    pk, ft, sc = to_host(packed), to_host(fp8_t), eng.scale_tensor().cpu().numpy()
+    assert np.array_equal(t16[segs.slice_of("blk0.wq")], bf16_bits_from_f32(gp[segs.slice_of("blk0.wq")]))
+    for layer in range(2):
+        want = np.concatenate([bf16_bits_from_f32(gp[segs.slice_of(f"blk{layer}.{w}")]).reshape(D, D)
+                               for w in ("wq", "wk", "wv")], axis=1)
+        assert np.array_equal(pk[layer * 3 * D * D:(layer + 1) * 3 * D * D].reshape(D, 3 * D), want)
+    seen = 0
+    for i, name in enumerate(segs.names):
+        if not (segs.flags[i] & SEG_TWIN_FP8):
+            continue
+        sl = segs.slice_of(name)
+        amax, scale, q = oracle.fp8_quant(gp[sl])
+        a = aux[i]
+        assert np.float32(sc[i]) == np.float32(scale)
+        got = ft[a.fp8_t_off:a.fp8_t_off + a.rows * a.cols].reshape(a.cols, a.rows)
+        assert np.array_equal(got, q.reshape(a.rows, a.cols).T), name
+        assert not t8[sl].any()                                   # the row-major twin of these is not written
+        seen += 1
+    assert seen == 6
+    # bad tables are refused
+    aux[0].rows, aux[0].cols, aux[0].pack_ld = 3, 5, 8
+    with pytest.raises(Exception):
+        eng.set_derived(aux, packed, fp8_t)
+    eng.close()
