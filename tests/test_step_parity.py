@@ -227,3 +227,52 @@ def test_derived_twins_packed_qkv_and_transposed_fp8(oracle, split):
     with pytest.raises(Exception):
         eng.set_derived(aux, packed, fp8_t)
     eng.close()
+
+
+@pytest.mark.parametrize("n", [1, 3, 1023, 1025])
+def test_tiny_and_ragged_sizes(oracle, n):
+    """Sizes below and around one chunk (1024 elements): everything goes through the element-wise path."""
+    p, g, m, v = make_inputs(n, seed=100 + n, grad_dtype=DT_BF16, state_dtype=DT_BF16)
+    kw = dict(HYP, wd=0.1, clip=0.5, grad_scale=1.0, t_before=9)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, None, p, g, m, v, check_finite=True, **kw)
+    out = run_gpu(None, p, g, m, v, dict(HYP, wd=0.1, clip=0.5, grad_scale=1.0, t=10), n_arena=n)
+    assert abs(out["status"].norm - info["norm"]) <= 1e-12 * info["norm"] + 1e-300
+    clipped = info["norm"] > 0.5
+    assert np.abs(out["m"].astype(np.int64) - rm.astype(np.int64)).max() <= (1 if clipped else 0)
+    assert np.abs(out["v"].astype(np.int64) - rv.astype(np.int64)).max() <= (1 if clipped else 0)
+    from parity_util import bf16_to_f32
+    check_step(dict(p=out["p"], m=bf16_to_f32(out["m"]), v=bf16_to_f32(out["v"])), rp, bf16_to_f32(rm),
+               bf16_to_f32(rv), p, exact_moments=False)
+    assert np.array_equal(out["twin"], bf16_bits_from_f32(out["p"])) and not out["g"].any()
+
+
+def test_empty_shard_and_misaligned_buffers(oracle):
+    """An engine that owns nothing still launches (an empty ZeRO rank); buffers that are not
+    16-byte aligned take the element-wise path everywhere and give the same numbers."""
+    import torch
+    from anni_b200.engine import OptStep
+    from parity_util import to_dev, to_host
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    eng = OptStep(segs, grad_dtype=DT_F32, state_dtype=DT_F32, shard_off=n, shard_n=0).allocate()
+    eng.step_split(OptStep.hyper(**dict(HYP, wd=0.1, clip=1.0, t=3)))
+    st = eng.status()
+    assert st.error == 0 and st.norm == 0.0 and st.skipped == 0
+    eng.close()
+    p, g, m, v = make_inputs(n, seed=14)
+    kw = dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t_before=2)
+    (rp, rg, rm, rv), info = _oracle_step(oracle, segs, p, g, m, v, check_finite=True, **kw)
+    eng = OptStep(segs, grad_dtype=DT_F32, state_dtype=DT_F32)
+    bufs = [torch.zeros(n + 4, dtype=torch.float32, device="cuda")[1:n + 1] for _ in range(4)]   # 4 bytes off
+    twin = torch.zeros(n + 8, dtype=torch.bfloat16, device="cuda")[1:n + 1]                       # 2 bytes off
+    assert all(b.data_ptr() % 16 != 0 for b in bufs)
+    eng.bind(*bufs, twin)
+    for b, a in zip(bufs, (p, m, v, g)):
+        b.copy_(to_dev(a))
+    eng.step(OptStep.hyper(**dict(HYP, wd=0.1, clip=1.0, t=3)))
+    st = eng.status()
+    assert st.error == 0 and abs(st.norm - info["norm"]) <= 1e-12 * info["norm"]
+    out = dict(p=to_host(bufs[0]), m=to_host(bufs[1]), v=to_host(bufs[2]))
+    check_step(out, rp, rm, rv, p, exact_moments=not info["norm"] > 1.0)
+    assert np.array_equal(to_host(twin), bf16_bits_from_f32(out["p"])) and not to_host(bufs[3]).any()
+    eng.close()
