@@ -71,6 +71,8 @@ def lib():
     L.anni_optstep_set_derived.argtypes = [vp, vp, vp, vp]
     L.anni_optstep_set_peers.restype = i
     L.anni_optstep_set_peers.argtypes = [vp, vp, vp, vp, i, C.c_uint64]
+    L.anni_optstep_set_multicast.restype = i
+    L.anni_optstep_set_multicast.argtypes = [vp, vp, vp, vp, C.c_uint64]
     L.anni_optstep_reduce_norm.restype = i
     L.anni_optstep_reduce_norm.argtypes = [vp, C.POINTER(Hyper), vp]
     L.anni_optstep_selftest_barrier_timeout.restype = i

@@ -51,6 +51,41 @@ __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p)
 	return v;
 }
 
+/*
+** NVSwitch multicast ("multimem") accesses on a multicast address that maps the same buffer of
+** every GPU: the load returns the element-wise sum over all copies, reduced inside the switch
+** (bf16 pairs accumulated in float); the store lands in every copy.
+*/
+__device__ __forceinline__ uint4 mc_ld_reduce_bf16x8(const void *mc)
+{
+	uint4 r;
+
+	asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+	    : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+	return r;
+}
+
+__device__ __forceinline__ uint4 mc_ld_reduce_f32x4(const void *mc)
+{
+	uint4 r;
+
+	asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+	    : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+	return r;
+}
+
+__device__ __forceinline__ void mc_st_b64(void *mc, uint2 v)
+{
+	const unsigned long long x = ((unsigned long long)v.y << 32) | v.x;
+
+	asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" :: "l"(mc), "l"(x) : "memory");
+}
+
+__device__ __forceinline__ void mc_st_b32(void *mc, uint32_t v)
+{
+	asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" :: "l"(mc), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ float sqrt_approx(float x)
 {
 	float r;
@@ -547,8 +582,11 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 	io4<StateT>::store(a.m, e, m);
 	io4<StateT>::store(a.v, e, v);
 	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16) {
-		if (a.n_peers > 0) {
-			/* the all-gather, fused: this shard's twins straight into every rank's arena */
+		if (a.mc_twin) {
+			/* the all-gather, fused: ONE multicast store, replicated by the switch into every rank's arena */
+			mc_st_b64(a.mc_twin + e, make_uint2(pack_bf16x2(p.x[0], p.x[1]), pack_bf16x2(p.x[2], p.x[3])));
+		} else if (a.n_peers > 0) {
+			/* without multicast: this shard's twins stored into every rank's arena one by one */
 			for (int k = 0; k < a.n_peers; k++)
 				io4<__nv_bfloat16>::store(a.twin_peer[k], e, p);
 		} else
@@ -727,7 +765,9 @@ __device__ __forceinline__ void quantize_phase(const anni_launch &a)
 				    | ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x[2] * inv, p.x[3] * inv),
 				    __NV_SATFINITE, __NV_E4M3) << 16);
 
-				if (a.n_peers > 0) {
+				if (a.mc_twin8)
+					mc_st_b32(a.mc_twin8 + e, q);
+				else if (a.n_peers > 0) {
 					for (int k = 0; k < a.n_peers; k++)
 						__stcs(reinterpret_cast<uint32_t *>(a.twin8_peer[k] + e), q);
 				} else
@@ -839,6 +879,10 @@ template <> struct raw8<__nv_bfloat16> {
 	{
 		q = __ldcs(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + e));
 	}
+	__device__ __forceinline__ void load_mc(const void *mc, uint64_t e)
+	{
+		q = mc_ld_reduce_bf16x8(static_cast<const uint16_t *>(mc) + e);
+	}
 	__device__ __forceinline__ f32x8 widen() const
 	{
 		return unpack_bf16x8(q);
@@ -853,6 +897,11 @@ template <> struct raw8<float> {
 
 		q[0] = __ldcs(p);
 		q[1] = __ldcs(p + 1);
+	}
+	__device__ __forceinline__ void load_mc(const void *mc, uint64_t e)
+	{
+		q[0] = mc_ld_reduce_f32x4(static_cast<const float *>(mc) + e);
+		q[1] = mc_ld_reduce_f32x4(static_cast<const float *>(mc) + e + 4);
 	}
 	__device__ __forceinline__ f32x8 widen() const
 	{
@@ -922,7 +971,29 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) reduce_norm_kernel(const anni
 	uint64_t it = 0;
 	double s;
 
-	if (a.aligned && cb > 0) {
+	if (a.aligned && a.mc_grad) {
+		/* in-switch reduction: one multimem load per chunk returns the sum over all ranks */
+		for (; it + SLOTS <= w.iters; it += SLOTS) {
+			raw8<GradT> r[SLOTS];
+			uint64_t cmax = 0;
+
+			for (int ci = 0; ci < SLOTS; ci++)
+				cmax = max(cmax, walk_chunk(w, it + ci));
+			if ((cmax + 1) * ANNI_CHUNK > a.n)
+				break;
+#pragma unroll
+			for (int sl = 0; sl < SLOTS; sl++)
+				r[sl].load_mc(a.mc_grad, walk_chunk(w, it + sl) * ANNI_CHUNK + t8);
+#pragma unroll
+			for (int sl = 0; sl < SLOTS; sl++) {
+				const f32x8 sum = r[sl].widen();
+				const uint64_t e = walk_chunk(w, it + sl) * ANNI_CHUNK + t8;
+
+				io8<GradT>::store(a.grad, e, sum);
+				norm_accumulate<GradT>(sum, acc0, acc1);
+			}
+		}
+	} else if (a.aligned && cb > 0) {
 		for (; it + cb <= w.iters; it += cb) {
 			raw8<GradT> r[SLOTS];
 			uint64_t cmax = 0;

@@ -337,6 +337,9 @@ extern "C" int anni_optstep_set_peers(anni_optstep *h, const void *const *peer_g
 
 	if (!h || n_peers < 0 || n_peers > ANNI_MAX_PEERS)
 		return ANNI_E_ARG;
+	h->la.mc_grad = NULL;
+	h->la.mc_twin = NULL;
+	h->la.mc_twin8 = NULL;
 	if (n_peers == 0) {
 		h->la.n_peers = 0;
 		return ANNI_OK;
@@ -355,6 +358,21 @@ extern "C" int anni_optstep_set_peers(anni_optstep *h, const void *const *peer_g
 	if (bits & 15)
 		return ANNI_E_ARG;	/* peer arenas and the shard offset must keep 16-byte alignment */
 	h->la.n_peers = n_peers;
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_set_multicast(anni_optstep *h, const void *mc_grad, void *mc_twin,
+	void *mc_twin_fp8, uint64_t arena_off_padded)
+{
+	const size_t gsz = h && h->cfg.grad_dtype == ANNI_DT_BF16 ? 2u : 4u;
+
+	if (!h || h->la.n_peers < 1)
+		return ANNI_E_ARG;	/* peers first: the element-wise paths still use them */
+	h->la.mc_grad = mc_grad ? (const char *)mc_grad + arena_off_padded * gsz : NULL;
+	h->la.mc_twin = mc_twin ? (uint16_t *)mc_twin + arena_off_padded : NULL;
+	h->la.mc_twin8 = (mc_twin_fp8 && h->has_fp8) ? (uint8_t *)mc_twin_fp8 + arena_off_padded : NULL;
+	if (((uintptr_t)h->la.mc_grad | (uintptr_t)h->la.mc_twin | (uintptr_t)h->la.mc_twin8) & 15)
+		return ANNI_E_ARG;
 	return ANNI_OK;
 }
 

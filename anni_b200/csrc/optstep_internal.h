@@ -98,6 +98,14 @@ typedef struct anni_launch {
 	uint16_t	*twin_peer[ANNI_MAX_PEERS];
 	uint8_t		*twin8_peer[ANNI_MAX_PEERS];
 	int		n_peers;	/* world size when peer memory is in use, else 0 */
+	/*
+	** NVSwitch multicast addresses of the same arenas at this shard's offset (NULL: not in use).
+	** mc_grad: multimem.ld_reduce returns the sum over all ranks' copies, reduced in the switch;
+	** mc_twin / mc_twin8: multimem.st lands in every rank's copy.
+	*/
+	const void	*mc_grad;
+	uint16_t	*mc_twin;
+	uint8_t		*mc_twin8;
 	anni_control	*ctl;
 } anni_launch;
 

@@ -269,6 +269,13 @@ class OptStep:
               self.L.anni_optstep_set_peers(self.h, arr(peer_grad), arr(peer_twin), arr(peer_twin_fp8),
                                             n, int(arena_off_padded)))
 
+    def set_multicast(self, mc_grad, mc_twin, mc_twin_fp8, arena_off_padded):
+        """NVSwitch multicast addresses (ints, 0 = none) of the same arenas; call after set_peers."""
+        v = lambda x: C.c_void_p(int(x)) if x else None
+        check("anni_optstep_set_multicast",
+              self.L.anni_optstep_set_multicast(self.h, v(mc_grad), v(mc_twin), v(mc_twin_fp8),
+                                                int(arena_off_padded)))
+
     def reduce_norm(self, hp, stream=None):
         check("anni_optstep_reduce_norm",
               self.L.anni_optstep_reduce_norm(self.h, C.byref(hp), self._stream(stream)))

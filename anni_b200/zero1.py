@@ -34,6 +34,13 @@ has been read" barrier) and one small barrier at the end of the step::
     update kernel        decision + AdamW + twins stored into all ranks' arenas
     [all_reduce(max) of amax; quantise kernel with peer stores]      (fp8 twins only)
     barrier              every rank's twins have landed
+
+``multicast=True`` makes the same two kernels go through the NVSwitch multicast address of the
+arenas instead (``multimem.ld_reduce`` adds all ranks' copies in the switch, ``multimem.st``
+replicates a store into all of them).  It is off by default: a multicast group always includes
+the issuing GPU, so its own shard travels out and back over its link -- the busy direction
+carries the whole arena instead of (N-1)/N of it.  Measured at N = 2: 3.46 ms per step against
+2.09 ms with plain peer loads / stores.
 """
 import torch
 import torch.distributed as dist
@@ -65,7 +72,7 @@ class Zero1:
     """
 
     def __init__(self, segments, *, grad_dtype=DT_BF16, state_dtype=DT_F32, group=None,
-                 device=None, make_stepper=None, peer=None):
+                 device=None, make_stepper=None, peer=None, multicast=False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -91,6 +98,7 @@ class Zero1:
         if peer is None:
             peer = self.world > 1 and dev.type == "cuda" and hasattr(self.eng, "set_peers")
         self.peer = bool(peer) and self.world > 1
+        self.multicast = bool(multicast)        # use NVSwitch multicast addresses when the arenas have them
         self._tiny = torch.zeros(1, dtype=torch.float32, device=dev)
         if self.peer:
             self.grad_full, self._peer_grad = self._symm(self.padded, gdt)
@@ -99,7 +107,7 @@ class Zero1:
                 self.twin8_full, self._peer_twin8 = self._symm(self.padded, torch.uint8)
             else:
                 self.twin8_full, self._peer_twin8 = None, None
-            self.eng.set_peers(self._peer_grad, self._peer_twin, self._peer_twin8, self.rank * self.per)
+            self._attach_peers()
         else:
             self.grad_full = torch.zeros(self.padded, dtype=gdt, device=dev)
             self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
@@ -125,7 +133,17 @@ class Zero1:
         t = symm_mem.empty(n, dtype=dtype, device=self.device)
         t.zero_()
         hdl = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
-        return t, [int(p) for p in hdl.buffer_ptrs]
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.multicast else 0
+        return t, ([int(p) for p in hdl.buffer_ptrs], mc)
+
+    def _attach_peers(self):
+        off = self.rank * self.per
+        pg, pt = self._peer_grad, self._peer_twin
+        p8 = self._peer_twin8
+        self.eng.set_peers(pg[0], pt[0], p8[0] if p8 else None, off)
+        self.uses_multicast = bool(pg[1] and pt[1] and (p8 is None or p8[1]))
+        if self.uses_multicast:
+            self.eng.set_multicast(pg[1], pt[1], p8[1] if p8 else 0, off)
 
     def new_grad_arena(self):
         """Another full gradient arena (e.g. one per micro-step buffer); see use_grad_arena."""
@@ -139,7 +157,7 @@ class Zero1:
         self.grad_full = t
         if self.peer:
             self._peer_grad = ptrs
-            self.eng.set_peers(self._peer_grad, self._peer_twin, self._peer_twin8, self.rank * self.per)
+            self._attach_peers()
         elif self.world == 1:
             self.grad_shard = t[:self.per]
             self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard, self.twin8_shard)

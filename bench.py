@@ -211,7 +211,8 @@ def run_ours(args):
     segs = lm_segments(**LM_SHAPES[shape], wd="matrices", twin=twin_kind)
     n = segs.n
     assert args.workload != WORKLOAD or n == N_PARAMS
-    z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev)
+    z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev,
+              multicast=os.environ.get("ANNI_B200_MULTICAST", "0") == "1")
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     z.master.normal_(0, 0.02, generator=gen)
@@ -393,7 +394,8 @@ def run_ours(args):
         wire = (world - 1) / world * n * 2 / 1e9            # GB each way per GPU, per collective
         rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
         ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
-        line["nvlink"] = {"mode": "peer kernels" if z.peer else "nccl", "wire_gb_per_collective": wire,
+        line["nvlink"] = {"mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
+                                   else "peer kernels" if z.peer else "nccl"), "wire_gb_per_collective": wire,
                           "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,
                           "reduce_scatter_frac": (wire / 770.0 * 1e3) / rs_ms if rs_ms else None,
                           "all_gather_frac": (wire / 770.0 * 1e3) / ag_ms if ag_ms else None}

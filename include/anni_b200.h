@@ -215,6 +215,16 @@ int	anni_optstep_set_derived(anni_optstep *h, const anni_seg_derived *aux, void 
 int	anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad, void *const *peer_twin,
 		void *const *peer_twin_fp8, int n_peers, uint64_t arena_off_padded);
 int	anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
+/*
+** Optional, after anni_optstep_set_peers: NVSwitch multicast addresses of the same three arenas
+** (element 0 of the padded arena; NULL for any that has none).  The reduce kernel then issues one
+** multimem.ld_reduce per vector (the switch adds all ranks' copies; bf16 accumulated in float) and
+** the update / quantise phases one multimem.st per vector (the switch replicates it into every
+** rank's arena) instead of N peer loads / stores: each GPU's link carries its own shard once in
+** the light direction.  A later anni_optstep_set_peers clears them.
+*/
+int	anni_optstep_set_multicast(anni_optstep *h, const void *mc_grad, void *mc_twin,
+		void *mc_twin_fp8, uint64_t arena_off_padded);
 
 /* Blocks until `stream` has finished the queued steps, then copies the status. */
 int	anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *stream);

@@ -22,22 +22,25 @@ def _world():
     return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 0
 
 
-@pytest.mark.parametrize("peer", [1, 0])
+@pytest.mark.parametrize("mode", ["mc", "peer", "nccl"])
 @pytest.mark.parametrize("twin,state", [("bf16", "f32"), ("bf16", "bf16"), ("fp8", "f32")])
-def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state, peer):
-    """peer=1: reduce-scatter and all-gather fused into the kernels over peer memory;
-    peer=0: the same step around NCCL reduce-scatter / all-gather."""
+def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state, mode):
+    """mc: reduce-scatter and all-gather fused into the kernels through NVSwitch multicast
+    (multimem.ld_reduce / multimem.st); peer: the same with plain peer loads / stores;
+    nccl: the same step around NCCL reduce-scatter / all-gather."""
     world = _world()
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ANNI_TEST_PEER=str(peer))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ANNI_TEST_MODE=mode)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300),
            os.path.join(ROOT, "tests", "zero1_gpu_worker.py"), str(tmp_path), twin, state]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stderr[-3000:]
     z = np.load(tmp_path / f"zero1_gpu_{twin}_{state}.npz")
-    assert int(z["peer"]) == peer
+    assert int(z["peer"]) == int(mode != "nccl")
+    if mode != "mc":
+        assert int(z["multicast"]) == 0
     segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin=twin)
     n = segs.n
     rng = np.random.default_rng(321)

@@ -26,7 +26,8 @@ def main():
     segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin=twin)
     n = segs.n
     sd = DT_BF16 if state == "bf16" else DT_F32
-    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev, peer=os.environ.get("ANNI_TEST_PEER", "1") == "1")
+    mode = os.environ.get("ANNI_TEST_MODE", "mc")
+    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev, peer=mode != "nccl", multicast=mode == "mc")
     rng = np.random.default_rng(321)
     p = rng.normal(0, 0.02, n).astype(np.float32)
     m = rng.normal(0, 1e-4, n).astype(np.float32)
@@ -56,7 +57,7 @@ def main():
     all_stats = [None] * world
     dist.all_gather_object(all_stats, stats)
     if rank == 0:
-        np.savez(os.path.join(out_dir, f"zero1_gpu_{twin}_{state}.npz"), peer=int(z.peer), p=to_host(full_p), m=to_host(full_m),
+        np.savez(os.path.join(out_dir, f"zero1_gpu_{twin}_{state}.npz"), peer=int(z.peer), multicast=int(getattr(z, "uses_multicast", False)), p=to_host(full_p), m=to_host(full_m),
                  v=to_host(full_v), twin=to_host(z.twin_full[:n]),
                  twin8=to_host(z.twin8_full[:n]) if z.twin8_full is not None else np.zeros(1, np.uint8),
                  scale=z.eng.scale_tensor().cpu().numpy(), stats=np.array(all_stats, dtype=np.float64),
