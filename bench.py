@@ -160,7 +160,7 @@ def run_reference(args):
         "impl": "reference", "metric": "adam_step_params_per_s", "value": base["value"],
         "unit": "params/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f64",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "n_params": N_PARAMS, "sample_params": sample,
                    "note": "reference CPU host loop (double math, fp32 storage), single-threaded "
@@ -367,7 +367,7 @@ def run_ours(args):
     line = {
         "metric": "adam_step_params_per_s", "value": value, "unit": "params/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64+f32",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64+f32",
         "data": "synthetic",
         "config": {"workload": args.workload, "n_params": n, "grads": gdt_name, "master": "fp32",
                    "moments": sdt_name, "twins": twin_kind, "clip": HYPER["clip"], "wd": "0.1 on matrices",
