@@ -5,7 +5,7 @@
 
 One "step" is one pass of the hot path over the whole packed arena: gradient norm,
 clip / skip decision, AdamW, fp32 master, bf16 moments, bf16 weight twins, gradient
-zeroing.  Workload (BASELINE configuration "run555m"): 555,762,080 parameters in the
+zeroing.  Workload (the headline configuration, "run555m"): 555,762,080 parameters in the
 reference's tensor list, bf16 gradients N(0, 5e-4) with 0.1 % entries x100, fp32
 master, bf16 m/v, bf16 twins, clip 1.0 (active), weight decay 0.1 on matrices.  All
 data are synthetic and seeded; K + W gradient arenas are resident before timing, so no

@@ -12,8 +12,9 @@
 **
 ** Differences, all on purpose:
 **  - the tensor list is passed in as an array (the reference walks its `lm`
-**    model struct, lang/lm_adam.c:117-136; INTEGRATION.md shows the loop that
-**    builds the array from an `lm`), each tensor with a decay / twin flag;
+**    model struct, lang/lm_adam.c:117-136; the caller lists w_head, b_head, the
+**    embedding when untied, then each block's tensors in that order), each tensor
+**    with a decay / twin flag;
 **  - parameters, gradients and moments live in device flats for good (bias and
 **    LayerNorm vectors included: the reference re-uploads those every step,
 **    lang/lm_adam.c:361-429); host copies are refreshed by sync_host;
