@@ -182,6 +182,90 @@ class Zero1:
         dist.all_gather_into_tensor(out, shard.contiguous(), group=self.group)
         return out[:self.n_arena]
 
+    # -- checkpoints in the reference trainer's format, from / to the sharded state ------
+    def _shards_to_rank0(self, shard):
+        """This buffer's shards as one fp32 host array in arena order on rank 0 (None elsewhere):
+        one shard at a time travels to rank 0, so no rank ever holds a second full copy on its device."""
+        import numpy as np
+        own = shard_geometry(self.n_arena, self.world)[1]
+        full = np.empty(self.n_arena, np.float32) if self.rank == 0 else None
+        mine = shard[:self.per].float()
+        for r, (off, cnt) in enumerate(own):
+            if cnt == 0:
+                continue
+            if r == 0:
+                if self.rank == 0:
+                    full[off:off + cnt] = mine[:cnt].cpu().numpy()
+            elif self.rank == r:
+                dist.send(mine[:cnt].contiguous(), dst=dist.get_global_rank(self.group, 0)
+                          if self.group is not None else 0, group=self.group)
+            elif self.rank == 0:
+                tmp = torch.empty(cnt, dtype=torch.float32, device=self.device)
+                dist.recv(tmp, src=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                          group=self.group)
+                full[off:off + cnt] = tmp.cpu().numpy()
+        return full
+
+    def _shards_from_rank0(self, full, shard):
+        """The inverse: rank 0 hands every rank its slice of a full fp32 host array."""
+        own = shard_geometry(self.n_arena, self.world)[1]
+        for r, (off, cnt) in enumerate(own):
+            if cnt == 0:
+                continue
+            if self.rank == 0:
+                piece = torch.from_numpy(full[off:off + cnt]).to(self.device)
+                if r == 0:
+                    shard[:cnt].copy_(piece)
+                else:
+                    dist.send(piece, dst=dist.get_global_rank(self.group, r) if self.group is not None else r,
+                              group=self.group)
+            elif self.rank == r:
+                tmp = torch.empty(cnt, dtype=torch.float32, device=self.device)
+                dist.recv(tmp, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                          group=self.group)
+                shard[:cnt].copy_(tmp)
+
+    def save_checkpoint(self, path, info, *, t, epoch=0, step=0, merges=None):
+        """lm_save_checkpoint (lang/lm_serialize.c:302-331 of the reference) from the sharded
+        state: weights, m and v of all ranks in optimizer order, written by rank 0 in the
+        reference's byte layout (``info``: an anni_b200.checkpoint.CkptModel with the model's
+        dimensions and kind).  Collective: every rank calls it."""
+        from . import checkpoint
+        w = self._shards_to_rank0(self.master)
+        m = self._shards_to_rank0(self.m)
+        v = self._shards_to_rank0(self.v)
+        if self.rank == 0:
+            info.n, info.has_adam, info.t, info.epoch, info.step = self.n_arena, 1, int(t), int(epoch), int(step)
+            checkpoint.save_model(path, info, w, m, v, merges)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def load_checkpoint(self, path):
+        """lm_load_checkpoint (lang/lm_serialize.c:526-587) into the sharded state: rank 0 reads
+        the file, every rank receives its slice of the weights, m and v (rounded to the moment
+        dtype) and rebuilds its bf16 twins.  Returns (t, epoch, step).  Collective."""
+        from . import checkpoint
+        head = torch.zeros(4, dtype=torch.int64, device=self.device)
+        ck = None
+        if self.rank == 0:
+            ck = checkpoint.load_model(path)
+            k = ck["info"]
+            ok = k.n == self.n_arena and bool(k.has_adam)
+            head.copy_(torch.tensor([1 if ok else 0, k.t, k.epoch, k.step], dtype=torch.int64))
+        if self.world > 1:
+            dist.broadcast(head, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                           group=self.group)
+        ok, t, epoch, step = (int(x) for x in head.tolist())
+        if not ok:
+            raise ValueError(f"{path}: slot count or Adam section does not match this arena "
+                             f"({self.n_arena} parameters)")
+        for key, dst in (("w", self.master), ("m", self.m), ("v", self.v)):
+            self._shards_from_rank0(ck[key] if ck is not None else None, dst)
+        self.twin_shard.copy_(self.master.to(torch.bfloat16))
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.twin_full, self.twin_shard.contiguous(), group=self.group)
+        return t, epoch, step
+
     # -- the step ------------------------------------------------------------------------
     def step(self, hp, record=None, grads_complete=False):
         """One sharded step.  ``record`` (optional) is called with a phase name after each

@@ -177,6 +177,15 @@ def run_reference(args):
 # our arm
 # ----------------------------------------------------------------------------------------
 
+def percentiles(xs):
+    """p10 / p50 / p90 of the per-step device times (this rank's events), ms."""
+    if not xs:
+        return None
+    xs = sorted(xs)
+    pick = lambda q: xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
+    return {"p10": pick(0.1), "p50": pick(0.5), "p90": pick(0.9), "n": len(xs)}
+
+
 def fill_grads(buf, n, seed, device):
     import torch
     gen = torch.Generator(device=device)
@@ -258,6 +267,7 @@ def run_ours(args):
         done = 0            # arenas are not consumed: no refills between batches
     total_ms, launches0 = 0.0, kernel_launches()
     phase_ms = {}
+    step_ms = []
     left = K
     wall0 = time.time()
     while left > 0:
@@ -286,12 +296,22 @@ def run_ours(args):
                 marks.append(evs)
             else:
                 z.step(hyper(t))
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append(e)
             t += 1
             done += 1
         e1.record()
         barrier()
         total_ms += e0.elapsed_time(e1)
+        if world == 1:
+            prev = e0
+            for e in marks:
+                step_ms.append(prev.elapsed_time(e))
+                prev = e
+            marks = []
         for evs in marks:
+            step_ms.append(evs[0].elapsed_time(evs[-1][1]))
             prev = evs[0]
             for name, e in evs[1:]:
                 phase_ms[name] = phase_ms.get(name, 0.0) + prev.elapsed_time(e)
@@ -386,6 +406,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": int(z.padded * z.grad_full.element_size()), "d2h_bytes_per_step": 48,
                 "steps": e2e_steps},
         "gpu_launches": int(launches),
+        "step_ms": percentiles(step_ms),
         "clocks": clocks,
         "status": {"norm": st.norm, "skipped": int(st.skipped), "error": int(st.error)},
     }

@@ -26,7 +26,7 @@ def test_shard_geometry():
     assert own1 == [(0, 100)]
 
 
-def test_two_gloo_ranks_match_single_process_oracle(oracle, tmp_path):
+def test_two_gloo_ranks_match_single_process_oracle(oracle, reflib, tmp_path):
     port = 29500 + (os.getpid() % 400)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
@@ -62,3 +62,15 @@ def test_two_gloo_ranks_match_single_process_oracle(oracle, tmp_path):
     dm = np.abs(z["m"].view(np.int32).astype(np.int64) - m.view(np.int32).astype(np.int64))
     assert dp.max() <= 1 and dm.max() <= 1 and (dp == 0).mean() > 0.999 and (dm == 0).mean() > 0.999
     assert np.array_equal(z["twin"], oracle.bf16_rne(z["p"]))
+    # the checkpoint the two ranks wrote together: reloaded shard-wise by a fresh pair of ranks,
+    # byte-identical to the single-process writer, and accepted by the reference's own loader
+    from anni_b200 import checkpoint
+    assert int(z["ckpt_round_trip"]) == 1
+    ck = checkpoint.load_model(str(tmp_path / "zero1.ckpt"))
+    assert (ck["info"].t, ck["info"].epoch, ck["info"].step, ck["info"].n) == (3, 1, 3, n)
+    assert np.array_equal(ck["w"], z["p"]) and np.array_equal(ck["m"], z["m"]) and np.array_equal(ck["v"], z["v"])
+    single = str(tmp_path / "single.ckpt")
+    checkpoint.save_model(single, ck["info"], z["p"], z["m"], z["v"], ck["merges"])
+    assert open(single, "rb").read() == open(tmp_path / "zero1.ckpt", "rb").read()
+    back = reflib.ckpt_load_full(str(tmp_path / "zero1.ckpt"), n)
+    assert back["t"] == 3 and np.array_equal(back["w"], z["p"]) and np.array_equal(back["v"], z["v"])

@@ -39,6 +39,7 @@ def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state
     assert res.returncode == 0, res.stderr[-3000:]
     z = np.load(tmp_path / f"zero1_gpu_{twin}_{state}.npz")
     assert int(z["peer"]) == int(mode != "nccl")
+    assert int(z["ckpt_round_trip"]) == 1
     if mode != "mc":
         assert int(z["multicast"]) == 0
     segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin=twin)
@@ -86,3 +87,49 @@ def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state
             assert np.array_equal(z["twin8"][sl], q)
         else:
             assert np.array_equal(z["twin"][sl], bf16_bits_from_f32(z["p"][sl]))
+
+
+@pytest.mark.parametrize("state", ["f32", "bf16"])
+def test_checkpoint_out_of_and_into_the_device_state(reflib, tmp_path, state):
+    """One rank: two device steps, lm_save_checkpoint's bytes from the device state, the
+    reference's loader reads them back, and a fresh engine resumes with identical bits."""
+    from anni_b200 import checkpoint
+    from anni_b200.capi import DT_BF16, DT_F32
+    from anni_b200.engine import OptStep
+    from anni_b200.zero1 import Zero1
+    dev = torch.device("cuda", 0)
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    sd = DT_BF16 if state == "bf16" else DT_F32
+    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    z.master.normal_(0, 0.02, generator=gen)
+    for step in range(2):
+        z.grad_full[:n].copy_(torch.randn(n, device=dev, generator=gen).mul_(1e-3))
+        z.step(OptStep.hyper(lr=3e-4, t=step + 1, beta2=0.95, wd=0.1, clip=1.0))
+    k = checkpoint.CkptModel()
+    k.kind, k.tied, k.d_model, k.n_heads, k.d_ff, k.max_ctx, k.n_blocks = 1, 0, 64, 4, 256, 2048, 2
+    k.vocab, k.n_merges, k.merges_word = 300, 40, 40
+    merges = np.array([[4 + (2 * i) % 256, 4 + (2 * i + 1) % 256] for i in range(40)], np.int32)
+    path = str(tmp_path / "dev.ckpt")
+    z.save_checkpoint(path, k, t=2, epoch=0, step=2, merges=merges)
+    back = reflib.ckpt_load_full(path, n)
+    assert (back["n"], back["t"], back["step"]) == (n, 2, 2)
+    assert np.array_equal(back["w"], z.master[:n].cpu().numpy())
+    assert np.array_equal(back["m"], z.m[:n].float().cpu().numpy())
+    assert np.array_equal(back["v"], z.v[:n].float().cpu().numpy())
+    z2 = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev)
+    assert z2.load_checkpoint(path) == (2, 0, 2)
+    for a, b in ((z.master, z2.master), (z.m, z2.m), (z.v, z2.v), (z.twin_shard, z2.twin_shard)):
+        assert torch.equal(a[:n], b[:n])
+    # both continue with the same gradients and stay identical
+    g = torch.randn(n, device=dev, generator=gen).mul_(1e-3)
+    for zz in (z, z2):
+        zz.grad_full[:n].copy_(g)
+        zz.step(OptStep.hyper(lr=3e-4, t=3, beta2=0.95, wd=0.1, clip=1.0))
+    assert torch.equal(z.master, z2.master) and torch.equal(z.v, z2.v)
+    with pytest.raises(ValueError):
+        other = Zero1(lm_segments(**dict(LM_SHAPES["tiny"], vocab=260), wd="matrices"),
+                      grad_dtype=DT_BF16, state_dtype=sd, device=dev)
+        other.load_checkpoint(path)

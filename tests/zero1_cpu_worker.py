@@ -109,9 +109,26 @@ def main():
         results.append(z.status())
     full_p = z.gather_full(z.master)
     full_m = z.gather_full(z.m)
+    full_v = z.gather_full(z.v)
+    # checkpoint out of the sharded state, and back into a fresh one
+    from anni_b200 import checkpoint
+    k = checkpoint.CkptModel()
+    k.kind, k.tied, k.d_model, k.n_heads, k.d_ff, k.max_ctx, k.n_blocks = 1, 0, 64, 4, 256, 2048, 2
+    k.vocab, k.n_merges, k.merges_word = 300, 40, 40
+    merges = np.array([[4 + (2 * i) % 256, 4 + (2 * i + 1) % 256] for i in range(40)], np.int32)
+    path = os.path.join(out_dir, "zero1.ckpt")
+    z.save_checkpoint(path, k, t=3, epoch=1, step=3, merges=merges)
+    z2 = Zero1(segs, grad_dtype=DT_BF16, state_dtype=DT_F32, device=torch.device("cpu"),
+               make_stepper=lambda off, cnt: OracleStepper(segs, off, cnt))
+    counters = z2.load_checkpoint(path)
+    same = all(torch.equal(a[:z.shard_n], b[:z.shard_n]) for a, b in
+               ((z.master, z2.master), (z.m, z2.m), (z.v, z2.v), (z.twin_shard, z2.twin_shard)))
+    flags = torch.tensor([1 if same and counters == (3, 1, 3) else 0])
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     full_twin = z.twin_full[:n].clone()
     if rank == 0:
         np.savez(os.path.join(out_dir, "zero1_out.npz"), p=full_p.numpy(), m=full_m.numpy(),
+                 v=full_v.numpy(), ckpt_round_trip=int(flags.item()),
                  twin=_np(full_twin), norms=np.array([r["norm"] for r in results]),
                  skipped=np.array([r["skipped"] for r in results]), per=z.per, world=world)
     dist.destroy_process_group()

@@ -53,6 +53,20 @@ def main():
     full_p = z.gather_full(z.master)
     full_m = z.gather_full(z.m)
     full_v = z.gather_full(z.v)
+    # checkpoint written by all ranks together and read back shard-wise into a fresh engine
+    from anni_b200 import checkpoint
+    k = checkpoint.CkptModel()
+    k.kind, k.tied, k.d_model, k.n_heads, k.d_ff, k.max_ctx, k.n_blocks = 1, 0, 64, 4, 256, 2048, 2
+    k.vocab, k.n_merges, k.merges_word = 300, 40, 40
+    merges = np.array([[4 + (2 * i) % 256, 4 + (2 * i + 1) % 256] for i in range(40)], np.int32)
+    path = os.path.join(out_dir, f"zero1_gpu_{twin}_{state}.ckpt")
+    z.save_checkpoint(path, k, t=3, epoch=0, step=3, merges=merges)
+    z2 = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev, peer=False)
+    counters = z2.load_checkpoint(path)
+    same = counters == (3, 0, 3) and all(torch.equal(a[:z.shard_n], b[:z.shard_n]) for a, b in
+                                         ((z.master, z2.master), (z.m, z2.m), (z.v, z2.v)))
+    ck_ok = torch.tensor([1 if same else 0], device=dev)
+    dist.all_reduce(ck_ok, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
     all_stats = [None] * world
     dist.all_gather_object(all_stats, stats)
@@ -61,7 +75,7 @@ def main():
                  v=to_host(full_v), twin=to_host(z.twin_full[:n]),
                  twin8=to_host(z.twin8_full[:n]) if z.twin8_full is not None else np.zeros(1, np.uint8),
                  scale=z.eng.scale_tensor().cpu().numpy(), stats=np.array(all_stats, dtype=np.float64),
-                 world=world)
+                 world=world, ckpt_round_trip=int(ck_ok.item()))
     dist.destroy_process_group()
 
 
