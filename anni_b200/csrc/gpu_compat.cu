@@ -340,7 +340,7 @@ extern "C" int anni_grad_sumsq64(const void *d_x, int dtype, unsigned long long 
 	legacy_launch_base(&la, n);
 	la.grad = (void *)d_x;
 	la.aligned = ((uintptr_t)d_x & 15) == 0;
-	if (anni_launch_norm(&la, dtype, g_legacy.blocks, g_st) != ANNI_OK)
+	if (anni_launch_norm(&la, dtype, ANNI_DT_F32, g_legacy.blocks, g_st) != ANNI_OK)
 		return -1;
 	/* the reference returns the sum to the host with a blocking copy (gpu_cuda.cu:8532) */
 	if (cudaMemcpyAsync(out, (char *)g_legacy.ctl + offsetof(anni_control, reduce), sizeof(double),

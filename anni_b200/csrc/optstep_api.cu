@@ -232,7 +232,7 @@ extern "C" int anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, 
 
 	if (rc != ANNI_OK)
 		return rc;
-	return anni_launch_norm(&la, h->cfg.grad_dtype, h->blocks_split, (cudaStream_t)stream);
+	return anni_launch_norm(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, (cudaStream_t)stream);
 }
 
 extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)

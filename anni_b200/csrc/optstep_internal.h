@@ -118,8 +118,12 @@ typedef struct anni_launch {
 extern "C" {
 #endif
 
-/* Kernel launchers (optstep.cu).  `blocks` must not exceed ANNI_MAX_BLOCKS. */
-int	anni_launch_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
+/*
+** Kernel launchers (optstep.cu).  `blocks` is the resident grid (anni_grid_blocks, at most
+** ANNI_MAX_BLOCKS); norm / update / fused may launch fewer, the same number for the same
+** dtypes and step flags, so the two forms of the step share their block partials.
+*/
+int	anni_launch_norm(const anni_launch *a, int grad_dtype, int state_dtype, int blocks, cudaStream_t st);
 int	anni_launch_update(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
 		cudaStream_t st);
 int	anni_launch_fused(const anni_launch *a, int grad_dtype, int state_dtype, int blocks,
