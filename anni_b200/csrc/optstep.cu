@@ -86,19 +86,25 @@ __device__ __forceinline__ void mc_st_b32(void *mc, uint32_t v)
 	asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" :: "l"(mc), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ float sqrt_approx(float x)
+/*
+** The SFU's square root and reciprocal in their single-instruction forms.  These flush
+** subnormal inputs and results to zero; the caller keeps its operands out of that range by
+** scaling with powers of two (exact), which the forms without .ftz would do with extra
+** instructions around the same SFU operation.
+*/
+__device__ __forceinline__ float sqrt_approx_ftz(float x)
 {
 	float r;
 
-	asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+	asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
 	return r;
 }
 
-__device__ __forceinline__ float rcp_approx(float x)
+__device__ __forceinline__ float rcp_approx_ftz(float x)
 {
 	float r;
 
-	asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+	asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
 	return r;
 }
 
@@ -557,8 +563,15 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 		p = lrwd != 0.0f ? __double2float_rn(fma(-a.lrwdd, (double)p1, (double)p1)) : p1;
 		return;
 	}
-	const float den = __fadd_rn(sqrt_approx(__fmul_rn(v, a.ibc2)), a.eps);
-	const float upd = __fmul_rn(__fmul_rn(a.lrbc1, m), rcp_approx(den));
+	/*
+	** den = sqrt(v / bc2) + eps and upd = (lr / bc1 * m) / den, carried at other binary
+	** scales: s = sqrt(2^24 v / bc2) = 2^12 sqrt(v / bc2), so no subnormal v is flushed;
+	** den40 = 2^28 s + 2^40 eps = 2^40 den in one fused step (the same single rounding as
+	** the plain sum), never subnormal unless it is zero; the factor 2^40 returns through lr.
+	*/
+	const float s = sqrt_approx_ftz(__fmul_rn(v, a.ibc2_s24));
+	const float den40 = __fmaf_rn(s, 268435456.0f, a.eps_s40);
+	const float upd = __fmul_rn(__fmul_rn(a.lrbc1_s40, m), rcp_approx_ftz(den40));
 
 	p = __fsub_rn(p, upd);
 	p = __fmaf_rn(-lrwd, p, p);
@@ -1385,6 +1398,12 @@ extern "C" int anni_fill_hyper(anni_launch *a, const anni_optstep_hyper *hp)
 	a->epsd = hp->eps;
 	a->ibc2 = (float)(1.0 / bc2);
 	a->eps = (float)hp->eps;
+	/* the same three floats at the binary scales the fast update works in (exact products) */
+	a->ibc2_s24 = a->ibc2 * 16777216.0f;
+	a->eps_s40 = a->eps * 1099511627776.0f;
+	a->lrbc1_s40 = a->lrbc1 * 1099511627776.0f;
+	if (!isfinite(a->ibc2_s24) || !isfinite(a->eps_s40) || !isfinite(a->lrbc1_s40))
+		return ANNI_E_ARG;
 	a->lrwd = hp->weight_decay > 0.0 ? (float)(hp->lr * hp->weight_decay) : 0.0f;
 	a->flags = (a->flags & ~0xff) | (hp->flags & 0xff);
 	if (a->clip > 0.0 || (hp->flags & ANNI_STEP_CHECK_FINITE))

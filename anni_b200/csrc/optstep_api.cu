@@ -29,6 +29,7 @@ struct anni_optstep {
 	int			device;
 	int			blocks_coop;
 	int			blocks_split;
+	int			blocks_rn;	/* grid of the fused reduce-scatter + norm kernel */
 };
 
 static int derived_after_step(anni_optstep *h, const anni_launch *la, cudaStream_t st);
@@ -145,6 +146,16 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 		if (e && atoi(e) > 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount,
 		    h->device) == cudaSuccess && sms > 0 && atoi(e) * sms < h->blocks_coop)
 			h->blocks_coop = h->blocks_split = atoi(e) * sms;
+	}
+	h->blocks_rn = h->blocks_split;
+	{
+		/* ANNI_B200_RN_BLOCKS_PER_SM=k: resident blocks of the reduce-scatter + norm kernel (tuning knob) */
+		const char *e = getenv("ANNI_B200_RN_BLOCKS_PER_SM");
+		int sms = 0;
+
+		if (e && atoi(e) > 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount,
+		    h->device) == cudaSuccess && sms > 0 && atoi(e) * sms < h->blocks_rn)
+			h->blocks_rn = atoi(e) * sms;
 	}
 	h->la.n = cfg->shard_n;
 	h->la.arena_off = cfg->shard_off;
@@ -385,7 +396,7 @@ extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hype
 		return rc;
 	if (la.n_peers < 1)
 		return ANNI_E_ARG;
-	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_split, (cudaStream_t)stream);
+	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_rn, (cudaStream_t)stream);
 }
 
 extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)

@@ -85,6 +85,9 @@ typedef struct anni_launch {
 	double		lrwdd;		/* lr * weight_decay */
 	float		lrbc1;		/* lr / (1 - beta1^t) */
 	float		ibc2;		/* 1 / (1 - beta2^t) */
+	float		ibc2_s24;	/* ibc2 * 2^24, eps * 2^40, lrbc1 * 2^40: see adam_elem */
+	float		eps_s40;
+	float		lrbc1_s40;
 	float		eps;
 	float		lrwd;		/* lr * weight_decay */
 	/*
