@@ -82,10 +82,19 @@ int legacy_ready(void)
 	    || cudaMemset(g_legacy.ctl, 0, sizeof(anni_control)) != cudaSuccess
 	    || cudaMemcpy(g_legacy.seg_off, off, sizeof(off), cudaMemcpyHostToDevice) != cudaSuccess
 	    || cudaMemcpy(g_legacy.flags_twin, &f_twin, 4, cudaMemcpyHostToDevice) != cudaSuccess
-	    || cudaMemcpy(g_legacy.flags_plain, &f_plain, 4, cudaMemcpyHostToDevice) != cudaSuccess)
+	    || cudaMemcpy(g_legacy.flags_plain, &f_plain, 4, cudaMemcpyHostToDevice) != cudaSuccess
+	    || (g_legacy.blocks = anni_grid_blocks(ANNI_DT_F32, ANNI_DT_F32, 0)) < 1) {
+		/* all or nothing: a half-built state must not pass for a ready one at the next call */
+		(void)cudaGetLastError();
+		cudaFree(g_legacy.ctl);
+		cudaFree(g_legacy.seg_off);
+		cudaFree(g_legacy.flags_twin);
+		cudaFree(g_legacy.flags_plain);
+		cudaFree(g_legacy.amax);
+		memset(&g_legacy, 0, sizeof(g_legacy));
 		return -1;
-	g_legacy.blocks = anni_grid_blocks(ANNI_DT_F32, ANNI_DT_F32, 0);
-	return g_legacy.blocks > 0 ? 0 : -1;
+	}
+	return 0;
 }
 
 void legacy_launch_base(anni_launch *la, uint64_t n)

@@ -330,8 +330,13 @@ static int ensure_device(anni_lm_adam *opt)
 			return ANNI_E_NOMEM;
 		}
 		if (upload_as(opt->d_m, opt->state_dtype, opt->h_m, opt->n) != 0
-		    || upload_as(opt->d_v, opt->state_dtype, opt->h_v, opt->n) != 0)
+		    || upload_as(opt->d_v, opt->state_dtype, opt->h_v, opt->n) != 0) {
+			/* half-filled flats must not pass for moments at the next call */
+			cudaFree(opt->d_m);
+			cudaFree(opt->d_v);
+			opt->d_m = opt->d_v = NULL;
 			return ANNI_E_CUDA;
+		}
 		buf.master = opt->d_param;
 		buf.m = opt->d_m;
 		buf.v = opt->d_v;
@@ -384,11 +389,20 @@ extern "C" int anni_lm_adam_snapshot_begin(anni_lm_adam *opt)
 	if (!opt || !opt->d_m || !opt->d_v)
 		return ANNI_E_ARG;
 	if (!opt->snap_stream) {
+		st = NULL;
+		ev = NULL;
 		if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess
 		    || cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess
 		    || cudaMallocHost(&opt->snap_m, nb) != cudaSuccess
 		    || cudaMallocHost(&opt->snap_v, nb) != cudaSuccess) {
 			(void)cudaGetLastError();
+			if (opt->snap_m)
+				cudaFreeHost(opt->snap_m);
+			opt->snap_m = opt->snap_v = NULL;	/* snap_v is the last to be set: never left allocated */
+			if (ev)
+				cudaEventDestroy(ev);
+			if (st)
+				cudaStreamDestroy(st);
 			return ANNI_E_NOMEM;
 		}
 		opt->snap_stream = st;
@@ -561,8 +575,9 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	}
 	return ANNI_OK;
 fail:
+	/* params_valid stays as it is: a step refused for its arguments leaves the device weights the
+	** newest copy, and re-reading the host arrays would lose the steps taken so far */
 	opt->last_error = rc;
-	opt->params_valid = 0;
 	fprintf(stderr, "[adam] step %d: device step failed (%d); no host fallback in this library\n",
 	    opt->t, rc);
 	return rc;
