@@ -15,6 +15,7 @@ SEG_WD, SEG_TWIN_BF16, SEG_TWIN_FP8 = 1, 2, 4
 STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE, STEP_EXACT_UPDATE = 1, 2, 4, 8
 OK, E_ARG, E_CUDA, E_BARRIER_TIMEOUT, E_NOMEM, E_LIMIT = 0, -1, -2, -3, -4, -5
 NOALLOC_MAX_SEG = 1024
+RANGE_ACCUMULATE, RANGE_LAST, RANGE_LOCAL_TWINS, RANGE_FIRST = 1, 2, 4, 8
 
 
 class Config(C.Structure):
@@ -75,6 +76,14 @@ def lib():
     L.anni_optstep_set_multicast.argtypes = [vp, vp, vp, vp, C.c_uint64]
     L.anni_optstep_reduce_norm.restype = i
     L.anni_optstep_reduce_norm.argtypes = [vp, C.POINTER(Hyper), vp]
+    L.anni_optstep_reduce_norm_range.restype = i
+    L.anni_optstep_reduce_norm_range.argtypes = [vp, C.POINTER(Hyper), C.c_uint64, C.c_uint64, i, vp]
+    L.anni_optstep_update_range.restype = i
+    L.anni_optstep_update_range.argtypes = [vp, C.POINTER(Hyper), C.c_uint64, C.c_uint64, i, vp]
+    L.anni_optstep_quantize_ex.restype = i
+    L.anni_optstep_quantize_ex.argtypes = [vp, i, vp]
+    L.anni_peer_copy.restype = i
+    L.anni_peer_copy.argtypes = [vp, vp, C.c_size_t, vp]
     L.anni_optstep_selftest_barrier_timeout.restype = i
     L.anni_optstep_selftest_barrier_timeout.argtypes = [vp, C.c_uint, vp]
     L.anni_optstep_quantize.restype = i

@@ -910,6 +910,8 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) norm_kernel(const anni_launch
 		__threadfence();
 		t = sum_partials(a.ctl, (int)gridDim.x);
 		if (threadIdx.x == 0) {
+			if (a.flags & ANNI_LAUNCH_ACCUMULATE)	/* a later part of the same shard */
+				t += a.ctl->reduce[0];
 			a.ctl->reduce[0] = t;
 			a.ctl->reduce[1] = isfinite(t) ? 0.0 : 1.0;
 			a.ctl->norm_ticket = 0;
@@ -1108,6 +1110,8 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) reduce_norm_kernel(const anni
 		__threadfence();
 		t = sum_partials(a.ctl, (int)gridDim.x);
 		if (threadIdx.x == 0) {
+			if (a.flags & ANNI_LAUNCH_ACCUMULATE)	/* a later part of the same shard */
+				t += a.ctl->reduce[0];
 			a.ctl->reduce[0] = t;
 			a.ctl->reduce[1] = isfinite(t) ? 0.0 : 1.0;
 			a.ctl->norm_ticket = 0;
@@ -1134,7 +1138,8 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_laun
 		}
 	}
 	update_phase<GradT, StateT, EXACT>(a, d);
-	step_epilogue(a.ctl, d.skip);
+	if (!(a.flags & ANNI_LAUNCH_NO_EPILOGUE))
+		step_epilogue(a.ctl, d.skip);
 }
 
 /* The whole step in one cooperative launch. */

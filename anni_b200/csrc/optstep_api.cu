@@ -399,7 +399,101 @@ extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hype
 	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_rn, (cudaStream_t)stream);
 }
 
+/* a launch description restricted to elements [off, off + n) of the shard */
+static int restrict_range(const anni_optstep *h, anni_launch *la, uint64_t off, uint64_t n)
+{
+	const size_t gsz = h->cfg.grad_dtype == ANNI_DT_BF16 ? 2u : 4u;
+	const size_t ssz = h->cfg.state_dtype == ANNI_DT_BF16 ? 2u : 4u;
+	int k;
+
+	if ((off & 4095u) != 0 || off > h->cfg.shard_n || n > h->cfg.shard_n - off)
+		return ANNI_E_ARG;
+	la->n = n;
+	la->arena_off += off;
+	la->master += off;
+	la->m = (char *)la->m + off * ssz;
+	la->v = (char *)la->v + off * ssz;
+	la->grad = (char *)la->grad + off * gsz;
+	if (la->twin16)
+		la->twin16 += off;
+	if (la->twin8)
+		la->twin8 += off;
+	for (k = 0; k < la->n_peers; k++) {
+		la->peer_grad[k] = (const char *)la->peer_grad[k] + off * gsz;
+		la->twin_peer[k] += off;
+		if (la->twin8_peer[k])
+			la->twin8_peer[k] += off;
+	}
+	if (la->mc_grad)
+		la->mc_grad = (const char *)la->mc_grad + off * gsz;
+	if (la->mc_twin)
+		la->mc_twin += off;
+	if (la->mc_twin8)
+		la->mc_twin8 += off;
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_reduce_norm_range(anni_optstep *h, const anni_optstep_hyper *hp,
+	uint64_t elem_off, uint64_t elem_n, int flags, void *stream)
+{
+	anni_launch la;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	if (la.n_peers < 1)
+		return ANNI_E_ARG;
+	rc = restrict_range(h, &la, elem_off, elem_n);
+	if (rc != ANNI_OK)
+		return rc;
+	if (flags & ANNI_RANGE_ACCUMULATE)
+		la.flags |= ANNI_LAUNCH_ACCUMULATE;
+	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_rn, (cudaStream_t)stream);
+}
+
+extern "C" int anni_optstep_update_range(anni_optstep *h, const anni_optstep_hyper *hp,
+	uint64_t elem_off, uint64_t elem_n, int flags, void *stream)
+{
+	anni_launch la;
+	cudaStream_t st = (cudaStream_t)stream;
+	int rc = prepare(h, hp, &la);
+
+	if (rc != ANNI_OK)
+		return rc;
+	if (la.seg_aux)
+		return ANNI_E_ARG;	/* derived twins are a whole-arena, one-GPU feature */
+	rc = restrict_range(h, &la, elem_off, elem_n);
+	if (rc != ANNI_OK)
+		return rc;
+	if (flags & ANNI_RANGE_LOCAL_TWINS) {
+		la.n_peers = 0;
+		la.mc_twin = NULL;
+		la.mc_twin8 = NULL;
+	}
+	if (!(flags & ANNI_RANGE_LAST))
+		la.flags |= ANNI_LAUNCH_NO_EPILOGUE;
+	if ((flags & ANNI_RANGE_FIRST) && h->has_fp8
+	    && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st) != cudaSuccess)
+		return ANNI_E_CUDA;
+	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+}
+
+extern "C" int anni_peer_copy(void *dst, const void *src, size_t nbytes, void *stream)
+{
+	if (!dst || !src)
+		return ANNI_E_ARG;
+	if (nbytes == 0)
+		return ANNI_OK;
+	return cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDefault, (cudaStream_t)stream) == cudaSuccess
+	    ? ANNI_OK : ANNI_E_CUDA;
+}
+
 extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
+{
+	return anni_optstep_quantize_ex(h, 0, stream);
+}
+
+extern "C" int anni_optstep_quantize_ex(anni_optstep *h, int flags, void *stream)
 {
 	anni_launch la;
 	int rc;
@@ -410,6 +504,10 @@ extern "C" int anni_optstep_quantize(anni_optstep *h, void *stream)
 		return ANNI_OK;
 	la = h->la;
 	la.flags = ANNI_LAUNCH_HAS_FP8;
+	if (flags & ANNI_RANGE_LOCAL_TWINS) {
+		la.n_peers = 0;
+		la.mc_twin8 = NULL;
+	}
 	rc = anni_launch_quantize(&la, h->blocks_split, (cudaStream_t)stream);
 	return rc != ANNI_OK ? rc : derived_after_step(h, &la, (cudaStream_t)stream);
 }

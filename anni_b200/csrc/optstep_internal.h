@@ -116,6 +116,8 @@ typedef struct anni_launch {
 #define ANNI_LAUNCH_HOST_COEF	0x100	/* grad_scale is final: no norm, no decision (legacy two-call sequence) */
 #define ANNI_LAUNCH_NEED_NORM	0x200	/* the norm feeds a clip or a finite check */
 #define ANNI_LAUNCH_HAS_FP8	0x400	/* some segment asks for an e4m3 twin */
+#define ANNI_LAUNCH_ACCUMULATE	0x800	/* norm over a part of the shard: add to the running sum */
+#define ANNI_LAUNCH_NO_EPILOGUE	0x1000	/* update over a part of the shard that is not the last: the step stays open */
 
 #ifdef __cplusplus
 extern "C" {

@@ -280,8 +280,30 @@ class OptStep:
         check("anni_optstep_reduce_norm",
               self.L.anni_optstep_reduce_norm(self.h, C.byref(hp), self._stream(stream)))
 
-    def quantize(self, stream=None):
-        check("anni_optstep_quantize", self.L.anni_optstep_quantize(self.h, self._stream(stream)))
+    def quantize(self, stream=None, local_twins=False):
+        check("anni_optstep_quantize",
+              self.L.anni_optstep_quantize_ex(self.h, capi.RANGE_LOCAL_TWINS if local_twins else 0,
+                                              self._stream(stream)))
+
+    def reduce_norm_range(self, hp, off, n, accumulate, stream=None):
+        """reduce_norm over elements [off, off + n) of the shard; accumulate: add to the running sum."""
+        check("anni_optstep_reduce_norm_range",
+              self.L.anni_optstep_reduce_norm_range(self.h, C.byref(hp), int(off), int(n),
+                                                    capi.RANGE_ACCUMULATE if accumulate else 0,
+                                                    self._stream(stream)))
+
+    def update_range(self, hp, off, n, *, first, last, local_twins=True, stream=None):
+        """update over elements [off, off + n) of the shard (see anni_optstep_update_range)."""
+        flags = ((capi.RANGE_FIRST if first else 0) | (capi.RANGE_LAST if last else 0)
+                 | (capi.RANGE_LOCAL_TWINS if local_twins else 0))
+        check("anni_optstep_update_range",
+              self.L.anni_optstep_update_range(self.h, C.byref(hp), int(off), int(n), flags,
+                                               self._stream(stream)))
+
+    def peer_copy(self, dst_ptr, src_ptr, nbytes, stream=None):
+        """One asynchronous device copy between raw addresses (peer memory included)."""
+        check("anni_peer_copy", self.L.anni_peer_copy(C.c_void_p(int(dst_ptr)), C.c_void_p(int(src_ptr)),
+                                                      int(nbytes), self._stream(stream)))
 
     def step_split(self, hp, stream=None):
         """Same result through the three-launch form (what ZeRO-1 interleaves with collectives)."""

@@ -220,7 +220,9 @@ def run_ours(args):
     segs = lm_segments(**LM_SHAPES[shape], wd="matrices", twin=twin_kind)
     n = segs.n
     assert args.workload != WORKLOAD or n == N_PARAMS
+    mode = os.environ.get("ANNI_B200_ZERO1_MODE", "")          # "", "peer", "copy" or "nccl"
     z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev,
+              peer={"": None, "peer": True, "copy": "copy", "nccl": False}[mode],
               multicast=os.environ.get("ANNI_B200_MULTICAST", "0") == "1")
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
@@ -416,6 +418,7 @@ def run_ours(args):
         rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
         ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
         line["nvlink"] = {"mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
+                                   else "copy engines + local kernels" if getattr(z, "copy_mode", False)
                                    else "peer kernels" if z.peer else "nccl"), "wire_gb_per_collective": wire,
                           "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,
                           "reduce_scatter_frac": (wire / 770.0 * 1e3) / rs_ms if rs_ms else None,

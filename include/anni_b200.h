@@ -216,6 +216,35 @@ int	anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad, void *
 		void *const *peer_twin_fp8, int n_peers, uint64_t arena_off_padded);
 int	anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
 /*
+** The same two calls over a PART of the shard (elements [elem_off, elem_off + elem_n) of it,
+** elem_off a multiple of 4096), so that a caller can move the data with the copy engines and
+** overlap the copies of one part with the kernel of another: copy engines carry 771 GB/s per
+** direction over NVLink with both directions busy, loads issued by SMs 640 GB/s, stores 700 GB/s
+** (measured between two B200s).  Used that way, peer_grad[k] given to anni_optstep_set_peers
+** points at LOCAL copies of the peers' shards and the twins are stored locally, then pushed.
+**   anni_optstep_reduce_norm_range  flags: ANNI_RANGE_ACCUMULATE = add this part's sum of squares
+**                                   to the reduce buffer instead of replacing it (every part but
+**                                   the first)
+**   anni_optstep_update_range       flags: ANNI_RANGE_LAST = this part closes the step (loss-scale
+**                                   state machine, step counter); ANNI_RANGE_LOCAL_TWINS = store
+**                                   the twins through the bound buffers only, although peers are set;
+**                                   ANNI_RANGE_FIRST = clear the per-tensor amax (fp8 twins)
+**   anni_peer_copy                  one asynchronous copy between any two device addresses valid
+**                                   in this process (plain cudaMemcpyAsync; the driver picks the
+**                                   copy engine for peer memory)
+*/
+#define ANNI_RANGE_ACCUMULATE	1
+#define ANNI_RANGE_LAST		2
+#define ANNI_RANGE_LOCAL_TWINS	4
+#define ANNI_RANGE_FIRST	8
+int	anni_optstep_reduce_norm_range(anni_optstep *h, const anni_optstep_hyper *hp, uint64_t elem_off,
+		uint64_t elem_n, int flags, void *stream);
+int	anni_optstep_update_range(anni_optstep *h, const anni_optstep_hyper *hp, uint64_t elem_off,
+		uint64_t elem_n, int flags, void *stream);
+int	anni_peer_copy(void *dst, const void *src, size_t nbytes, void *stream);
+/* anni_optstep_quantize with ANNI_RANGE_LOCAL_TWINS: the e4m3 twins through the bound buffer only. */
+int	anni_optstep_quantize_ex(anni_optstep *h, int flags, void *stream);
+/*
 ** Optional, after anni_optstep_set_peers: NVSwitch multicast addresses of the same three arenas
 ** (element 0 of the padded arena; NULL for any that has none).  The reduce kernel then issues one
 ** multimem.ld_reduce per vector (the switch adds all ranks' copies; bf16 accumulated in float) and

@@ -22,11 +22,12 @@ def _world():
     return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 0
 
 
-@pytest.mark.parametrize("mode", ["mc", "peer", "nccl"])
+@pytest.mark.parametrize("mode", ["mc", "peer", "copy", "nccl"])
 @pytest.mark.parametrize("twin,state", [("bf16", "f32"), ("bf16", "bf16"), ("fp8", "f32")])
 def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state, mode):
     """mc: reduce-scatter and all-gather fused into the kernels through NVSwitch multicast
     (multimem.ld_reduce / multimem.st); peer: the same with plain peer loads / stores;
+    copy: copy engines pull the gradient shards and push the twins, the kernels work on local memory;
     nccl: the same step around NCCL reduce-scatter / all-gather."""
     world = _world()
     if world < 2:

@@ -27,7 +27,9 @@ def main():
     n = segs.n
     sd = DT_BF16 if state == "bf16" else DT_F32
     mode = os.environ.get("ANNI_TEST_MODE", "mc")
-    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev, peer=mode != "nccl", multicast=mode == "mc")
+    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=sd, device=dev,
+              peer="copy" if mode == "copy" else mode != "nccl", multicast=mode == "mc",
+              copy_parts=3)
     rng = np.random.default_rng(321)
     p = rng.normal(0, 0.02, n).astype(np.float32)
     m = rng.normal(0, 1e-4, n).astype(np.float32)
