@@ -35,18 +35,22 @@ has been read" barrier) and one small barrier at the end of the step::
     [all_reduce(max) of amax; quantise kernel with peer stores]      (fp8 twins only)
     barrier              every rank's twins have landed
 
-Copy mode (``peer="copy"``): the same arenas, but the data crosses NVLink on the copy engines.
-Measured between two B200s with both directions busy, copy engines carry 771 GB/s per direction,
-loads issued by SMs 640 GB/s and stores 700 GB/s, so for four and more ranks, where the step is
-NVLink-bound, this is the faster form::
+Copy mode (``peer="copy"``, opt-in): the same arenas, but the data crosses NVLink on the copy
+engines and the kernels work on local memory, part by part::
 
     [barrier]
-    copy stream: pull part p of this rank's shard out of every peer's gradient arena
-    main stream: reduce_norm over part p of the local copies          (overlaps pulls of p + 1)
+    copy streams: pull part p of this rank's shard out of every peer's gradient arena
+    main stream:  reduce_norm over part p of the local copies         (overlaps pulls of p + 1)
     all_reduce(sum)      2 doubles
-    main stream: update part p, twins stored locally
-    copy stream: push part p of the twins into every peer's arena     (overlaps update of p + 1)
+    main stream:  update part p, twins stored locally
+    copy streams: push part p of the twins into every peer's arena    (overlaps update of p + 1)
     barrier
+
+Between two B200s with both directions busy a copy engine carries 771 GB/s per direction against
+640 GB/s for loads and 700 GB/s for stores issued by SMs, but with every rank copying from / to
+all others at once the engines reach 685-705 GB/s, and the extra pass over local memory and the
+hand-offs between streams use that up: 2.40 ms against 2.09 ms per step at N = 2 (where the step
+is bound by local memory), 2.78 against 2.69 ms at N = 4.  The fused kernels stay the default.
 
 ``multicast=True`` makes the same two kernels go through the NVSwitch multicast address of the
 arenas instead (``multimem.ld_reduce`` adds all ranks' copies in the switch, ``multimem.st``
@@ -124,7 +128,8 @@ class Zero1:
             if self.copy_mode:
                 # local landing area for the peers' copies of this shard, and a stream for the copies
                 self._stage = torch.zeros(self.world, self.per, dtype=gdt, device=dev)
-                self._copy_stream = torch.cuda.Stream(device=dev)
+                # one stream per peer, so that the copies to / from all peers run at the same time
+                self._copy_streams = [torch.cuda.Stream(device=dev) for _ in range(self.world - 1)]
                 n_parts = copy_parts if copy_parts else (4 if self.shard_n >= (4 << 20) else 1)
                 step = -(-max(self.shard_n, 1) // n_parts)
                 step = -(-step // SHARD_ALIGN) * SHARD_ALIGN
@@ -350,11 +355,12 @@ class Zero1:
 
     def _step_copy(self, hp, mark, grads_complete):
         """The step with the copy engines moving the data (see the module text)."""
-        eng, cs = self.eng, self._copy_stream
+        eng, streams = self.eng, self._copy_streams
         main = torch.cuda.current_stream(self.device)
         gsz = self.grad_full.element_size()
         base = self.rank * self.per                     # this shard inside every padded arena
-        others = [k for k in range(self.world) if k != self.rank]
+        # rank r starts with peer r + 1: at any moment every GPU serves a different peer
+        others = [(self.rank + j) % self.world for j in range(1, self.world)]
         pg, pt, p8 = self._peer_grad[0], self._peer_twin[0], self._peer_twin8
 
         def after(src, dst):
@@ -364,11 +370,12 @@ class Zero1:
 
         if not grads_complete:
             self._barrier()
-        after(main, cs)
+        for cs in streams:
+            after(main, cs)
         for i, (o, n) in enumerate(self._parts):
-            for k in others:
+            for k, cs in zip(others, streams):
                 eng.peer_copy(self._stage[k].data_ptr() + o * gsz, pg[k] + (base + o) * gsz, n * gsz, cs)
-            after(cs, main)
+                after(cs, main)
             eng.reduce_norm_range(hp, o, n, accumulate=i > 0)
         mark("reduce_scatter+norm")
         dist.all_reduce(eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)
@@ -376,16 +383,17 @@ class Zero1:
         last = len(self._parts) - 1
         for i, (o, n) in enumerate(self._parts):
             eng.update_range(hp, o, n, first=i == 0, last=i == last, local_twins=True)
-            after(main, cs)
-            for k in others:
+            for k, cs in zip(others, streams):
+                after(main, cs)
                 eng.peer_copy(pt[k] + (base + o) * 2, self.twin_full.data_ptr() + (base + o) * 2, n * 2, cs)
         if eng.has_fp8:
             dist.all_reduce(eng.amax_tensor(), op=dist.ReduceOp.MAX, group=self.group)
             eng.quantize(local_twins=True)
-            after(main, cs)
-            for k in others:
+            for k, cs in zip(others, streams):
+                after(main, cs)
                 eng.peer_copy(p8[0][k] + base, self.twin8_full.data_ptr() + base, self.shard_n, cs)
-        after(cs, main)
+        for cs in streams:
+            after(cs, main)
         mark("update+all_gather")
         self._barrier()
         mark("barrier")

@@ -217,11 +217,12 @@ int	anni_optstep_set_peers(anni_optstep *h, const void *const *peer_grad, void *
 int	anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
 /*
 ** The same two calls over a PART of the shard (elements [elem_off, elem_off + elem_n) of it,
-** elem_off a multiple of 4096), so that a caller can move the data with the copy engines and
-** overlap the copies of one part with the kernel of another: copy engines carry 771 GB/s per
-** direction over NVLink with both directions busy, loads issued by SMs 640 GB/s, stores 700 GB/s
-** (measured between two B200s).  Used that way, peer_grad[k] given to anni_optstep_set_peers
-** points at LOCAL copies of the peers' shards and the twins are stored locally, then pushed.
+** elem_off a multiple of 4096), so that a caller can pipeline the step with its own data
+** movement: e.g. copy engines pull the peers' copies of the shard into local memory part by
+** part (peer_grad[k] given to anni_optstep_set_peers then points at those LOCAL copies) and push
+** the locally stored twins out, each overlapping the kernel of the neighbouring part.  Measured
+** on B200s this is no faster than the kernels moving the data themselves (2.78 against 2.69 ms
+** per step at four ranks), so it is an option, not the default.
 **   anni_optstep_reduce_norm_range  flags: ANNI_RANGE_ACCUMULATE = add this part's sum of squares
 **                                   to the reduce buffer instead of replacing it (every part but
 **                                   the first)
