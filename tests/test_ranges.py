@@ -1,0 +1,83 @@
+"""The part-wise forms of the split step (anni_optstep_update_range / _reduce_norm_range):
+the same bits as the whole-shard launches, one step counted, one loss-scale transition."""
+import numpy as np
+import pytest
+import torch
+
+from anni_b200.capi import DT_BF16, DT_F32, AnniError
+from anni_b200.engine import LM_SHAPES, OptStep, lm_segments
+from parity_util import make_inputs, to_dev, to_host
+
+pytestmark = pytest.mark.gpu
+
+PARTS = [(0, 8192), (8192, 4096), (12288, None)]       # offsets are multiples of 4096
+
+
+def _engine(segs, gd, sd, p, g, m, v):
+    eng = OptStep(segs, grad_dtype=gd, state_dtype=sd).allocate()
+    eng.master.copy_(to_dev(p))
+    eng.grad.copy_(to_dev(g))
+    eng.m.copy_(to_dev(m))
+    eng.v.copy_(to_dev(v))
+    return eng
+
+
+@pytest.mark.parametrize("twin", ["bf16", "fp8"])
+@pytest.mark.parametrize("gd,sd", [(DT_BF16, DT_BF16), (DT_F32, DT_F32)])
+def test_update_in_parts_equals_update_of_the_whole_shard(gd, sd, twin):
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin=twin)
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=3, grad_dtype=gd, state_dtype=sd)
+    hp = OptStep.hyper(lr=3e-4, t=7, beta2=0.95, wd=0.1, clip=1.0, check_finite=True, dev_loss_scale=True)
+    whole = _engine(segs, gd, sd, p, g, m, v)
+    parts = _engine(segs, gd, sd, p, g, m, v)
+    for eng in (whole, parts):
+        eng.loss_scale_init(scale=1.0, growth_interval=1)       # every clean step doubles the scale
+    whole.step_split(hp)
+    parts.norm(hp)
+    cuts = [(o, (n - o) if ln is None else ln) for o, ln in PARTS]
+    for i, (o, ln) in enumerate(cuts):
+        parts.update_range(hp, o, ln, first=i == 0, last=i == len(cuts) - 1, local_twins=False)
+    if parts.has_fp8:
+        parts.quantize()
+    a, b = whole.status(), parts.status()
+    assert (a.norm, a.skipped, a.steps_done, a.loss_scale) == (b.norm, b.skipped, b.steps_done, b.loss_scale)
+    assert b.steps_done == 1 and b.loss_scale == 2.0             # the epilogue ran once, at the last part
+    for name in ("master", "m", "v", "grad", "twin_bf16", "twin_fp8"):
+        x, y = getattr(whole, name), getattr(parts, name)
+        if x is not None:
+            assert torch.equal(x, y), name
+    assert torch.equal(whole.scale_tensor(), parts.scale_tensor())
+    with pytest.raises(AnniError):
+        parts.update_range(hp, 100, 50, first=True, last=True)    # offset not a multiple of 4096
+    with pytest.raises(AnniError):
+        parts.update_range(hp, 4096, n, first=True, last=True)    # runs past the shard
+    whole.close()
+    parts.close()
+
+
+def test_reduce_norm_in_parts_accumulates_the_sum_of_squares():
+    """One rank standing for all: the "peer" arena is a second local buffer.  Part-wise
+    launches leave the same reduced gradients and the same sum of squares (to the last bits:
+    the partial sums are grouped differently) as one launch."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=4, grad_dtype=DT_BF16, state_dtype=DT_F32)
+    hp = OptStep.hyper(lr=3e-4, t=1, clip=1.0)
+    src = to_dev(g).clone()
+    twin_arena = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    out = []
+    for cuts in ([(0, n)], [(o, (n - o) if ln is None else ln) for o, ln in PARTS]):
+        eng = _engine(segs, DT_BF16, DT_F32, p, g, m, v)
+        eng.grad.zero_()
+        eng.set_peers([src.data_ptr()], [twin_arena.data_ptr()], None, 0)
+        for i, (o, ln) in enumerate(cuts):
+            eng.reduce_norm_range(hp, o, ln, accumulate=i > 0)
+        torch.cuda.synchronize()
+        out.append((to_host(eng.grad).copy(), eng.reduce_tensor().cpu().numpy().copy()))
+        eng.close()
+    assert np.array_equal(out[0][0], out[1][0]) and np.array_equal(out[0][0], to_host(src))
+    assert out[0][1][1] == out[1][1][1] == 0.0
+    assert abs(out[0][1][0] - out[1][1][0]) <= 1e-14 * out[0][1][0]
+    ref = float((to_host(src).astype(np.uint32) << 16).view(np.float32).astype(np.float64).__pow__(2).sum())
+    assert abs(out[1][1][0] - ref) <= 1e-12 * ref
