@@ -1241,19 +1241,24 @@ __global__ void __launch_bounds__(ANNI_THREADS) barrier_timeout_kernel(anni_cont
 /*
 ** e4m3 twins in the transposed [cols][rows] layout the forward GEMM wants
 ** (the reference's f32_transpose_to_fp8_kernel, one launch per tensor): here
-** one launch for every such tensor.  64x64 tiles, dealt round-robin over a
-** persistent grid; tile_prefix[s] = number of tiles before tensor s.  A tile is
-** read row-wise (256-byte rows of the fp32 master), quantised with the
-** tensor's scale, turned in shared memory and written column-wise as 64-byte rows.
+** one launch for every such tensor.  Tiles of ANNI_TT_R rows x ANNI_TT_C columns of the
+** master, dealt round-robin over a persistent grid; tile_prefix[s] = number of tiles
+** before tensor s.
+**
+** A whole, aligned tile (every tile of the LM shapes) goes the fast way: each thread reads
+** eight 128-bit pieces of master rows (256 contiguous bytes per tile row), quantises four
+** values into one 32-bit word and stores it in shared memory at [row][word ^ swizzle]; then
+** eight lanes gather one 128-byte row of the transposed tile, 16 bytes each, and store it
+** with one 128-bit access.  The swizzle (word index XOR 2 * (row / 16)) keeps both the
+** row-wise stores and the column-wise gathers free of bank conflicts.  Edge tiles and
+** unaligned tensors go element by element.
 */
-#define ANNI_TT	64
-
 __global__ void __launch_bounds__(ANNI_THREADS) quantize_transposed_kernel(const anni_launch a,
 	const int64_t *tile_prefix, int64_t n_tiles)
 {
-	__shared__ uint8_t tile[ANNI_TT][ANNI_TT + 4];
-	const int tx = threadIdx.x & 63;	/* column inside the tile when reading */
-	const int ty = threadIdx.x >> 6;	/* 4 rows per pass */
+	__shared__ uint32_t tile[ANNI_TT_R * (ANNI_TT_C / 4)];	/* 128 rows x 16 words of four e4m3 codes */
+	uint8_t *tile_b = reinterpret_cast<uint8_t *>(tile);		/* the same bytes, unswizzled, for edge tiles */
+	const int tid = threadIdx.x;
 	int seg = 0;
 
 	if (a.ctl->skipped)
@@ -1266,23 +1271,78 @@ __global__ void __launch_bounds__(ANNI_THREADS) quantize_transposed_kernel(const
 		while (seg + 1 < a.n_seg && tile_prefix[seg + 1] <= t)
 			seg++;
 		const anni_seg_derived ax = a.seg_aux[seg];
-		const int tiles_x = (ax.cols + ANNI_TT - 1) / ANNI_TT;
+		const int tiles_x = (ax.cols + ANNI_TT_C - 1) / ANNI_TT_C;
 		const int64_t lt = t - tile_prefix[seg];
-		const int r0 = (int)(lt / tiles_x) * ANNI_TT;
-		const int c0 = (int)(lt % tiles_x) * ANNI_TT;
+		const int r0 = (int)(lt / tiles_x) * ANNI_TT_R;
+		const int c0 = (int)(lt % tiles_x) * ANNI_TT_C;
 		const float inv = __fdiv_rn(1.0f, fp8_scale(a.seg_amax[seg]));
 		const float *src = a.master + ((uint64_t)a.seg_off[seg] - a.arena_off);
 		uint8_t *dst = a.fp8_t + ax.fp8_t_off;
+		const bool fast = r0 + ANNI_TT_R <= ax.rows && c0 + ANNI_TT_C <= ax.cols && (ax.cols & 3) == 0
+		    && (ax.rows & 15) == 0 && ((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 15) == 0;
 
-		for (int j = ty; j < ANNI_TT; j += ANNI_THREADS / 64)
-			if (r0 + j < ax.rows && c0 + tx < ax.cols)
-				tile[j][tx] = (uint8_t)__nv_cvt_float_to_fp8(
-				    src[(uint64_t)(r0 + j) * ax.cols + c0 + tx] * inv, __NV_SATFINITE, __NV_E4M3);
+		if (fast) {
+			const float *s0 = src + (uint64_t)r0 * ax.cols + c0;
+
+#pragma unroll
+			for (int half = 0; half < 2; half++) {
+				f32x4 v[4];
+
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					const int f = tid + ANNI_THREADS * (half * 4 + i);	/* 128-bit piece of the tile */
+
+					v[i] = io4<float>::load(s0 + (uint64_t)(f >> 4) * ax.cols, (uint64_t)(f & 15) * 4);
+				}
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					const int f = tid + ANNI_THREADS * (half * 4 + i);
+					const int r = f >> 4;
+
+					tile[r * 16 + ((f & 15) ^ (((r >> 4) & 7) << 1))] = e4m3x4(v[i], inv);
+				}
+			}
+			__syncthreads();
+#pragma unroll
+			for (int j = 0; j < 2; j++) {
+				const int id = tid + ANNI_THREADS * j;	/* 16-byte piece of the transposed tile */
+				const int c = id >> 3;			/* source column = destination row */
+				const int sg = id & 7;			/* source rows 16 sg .. 16 sg + 15 */
+				const int w = (c >> 2) ^ (sg << 1);
+				const uint32_t sel = (uint32_t)(c & 3) | ((4u + (uint32_t)(c & 3)) << 4);
+				uint32_t out[4];
+
+#pragma unroll
+				for (int k = 0; k < 4; k++) {
+					const uint32_t *row = &tile[(16 * sg + 4 * k) * 16 + w];
+					const uint32_t lo = __byte_perm(row[0], row[16], sel);	/* the column's byte of two rows */
+					const uint32_t hi = __byte_perm(row[32], row[48], sel);
+
+					out[k] = __byte_perm(lo, hi, 0x5410);
+				}
+				__stcs(reinterpret_cast<uint4 *>(dst + (uint64_t)(c0 + c) * ax.rows + r0 + 16 * sg),
+				    make_uint4(out[0], out[1], out[2], out[3]));
+			}
+			__syncthreads();
+			continue;
+		}
+		for (int i = tid; i < ANNI_TT_R * ANNI_TT_C; i += ANNI_THREADS) {
+			const int r = i / ANNI_TT_C;
+			const int c = i % ANNI_TT_C;
+
+			if (r0 + r < ax.rows && c0 + c < ax.cols)
+				tile_b[i] = (uint8_t)__nv_cvt_float_to_fp8(
+				    src[(uint64_t)(r0 + r) * ax.cols + c0 + c] * inv, __NV_SATFINITE, __NV_E4M3);
+		}
 		__syncthreads();
-		/* now tx walks the rows of the source (contiguous in the transposed destination) */
-		for (int j = ty; j < ANNI_TT; j += ANNI_THREADS / 64)
-			if (c0 + j < ax.cols && r0 + tx < ax.rows)
-				dst[(uint64_t)(c0 + j) * ax.rows + r0 + tx] = tile[tx][j];
+		/* now consecutive threads walk the rows of the source (contiguous in the transposed destination) */
+		for (int i = tid; i < ANNI_TT_R * ANNI_TT_C; i += ANNI_THREADS) {
+			const int c = i / ANNI_TT_R;
+			const int r = i % ANNI_TT_R;
+
+			if (c0 + c < ax.cols && r0 + r < ax.rows)
+				dst[(uint64_t)(c0 + c) * ax.rows + r0 + r] = tile_b[r * ANNI_TT_C + c];
+		}
 		__syncthreads();
 	}
 }

@@ -304,7 +304,8 @@ extern "C" int anni_optstep_set_derived(anni_optstep *h, const anni_seg_derived 
 		if (aux[i].fp8_t_off >= 0) {
 			if (!shaped || !(h->h_seg_flags[i] & ANNI_SEG_TWIN_FP8))
 				goto bad;
-			tiles += (int64_t)((aux[i].rows + 63) / 64) * ((aux[i].cols + 63) / 64);
+			tiles += (int64_t)((aux[i].rows + ANNI_TT_R - 1) / ANNI_TT_R)
+			    * ((aux[i].cols + ANNI_TT_C - 1) / ANNI_TT_C);
 			any_t = 1;
 		}
 	}

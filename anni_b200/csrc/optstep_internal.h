@@ -23,6 +23,9 @@
 #define ANNI_UVEC		4
 #define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
 #define ANNI_UCHUNK_LOG2	10
+/* tile of the transposed e4m3 twins: rows x columns of the master (kernel and host tile count) */
+#define ANNI_TT_R		128
+#define ANNI_TT_C		64
 #define ANNI_MAX_BLOCKS		2048	/* capacity of the per-block partial table */
 #define ANNI_MAX_PEERS		8	/* GPUs of one NVSwitch domain */
 /* polls of a bounded device wait before it gives up (each poll sleeps >= 32 ns) */

@@ -276,3 +276,37 @@ def test_empty_shard_and_misaligned_buffers(oracle):
     check_step(out, rp, rm, rv, p, exact_moments=not info["norm"] > 1.0)
     assert np.array_equal(to_host(twin), bf16_bits_from_f32(out["p"])) and not to_host(bufs[3]).any()
     eng.close()
+
+
+def test_transposed_fp8_twins_whole_and_edge_tiles(oracle):
+    """The transposed e4m3 twins for shapes that exercise the tiled path (whole 128 x 64 tiles,
+    128-bit accesses), the element-wise path (edge tiles, odd shapes) and both inside one tensor."""
+    import torch
+    from anni_b200 import capi
+    from anni_b200.capi import SEG_TWIN_FP8, SEG_WD
+    from anni_b200.engine import OptStep, Segments
+    from parity_util import to_dev, to_host
+    shapes = [(256, 128), (128, 64), (384, 192), (200, 100), (256, 96), (160, 64), (16, 4), (1536, 64)]
+    segs = Segments()
+    for i, (r, c) in enumerate(shapes):
+        segs.add(f"w{i}", r * c, SEG_WD | SEG_TWIN_FP8)
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=21, grad_dtype=DT_BF16)
+    eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_F32).allocate()
+    for t_, a_ in ((eng.master, p), (eng.grad, g), (eng.m, m), (eng.v, v)):
+        t_.copy_(to_dev(a_))
+    aux, off = [], 0
+    for r, c in shapes:
+        aux.append(capi.SegDerived(r, c, 0, 0, 0, off))
+        off += r * c
+    fp8_t = torch.full((off,), 0xAA, dtype=torch.uint8, device="cuda")
+    eng.set_derived(aux, None, fp8_t)
+    eng.step(OptStep.hyper(**dict(HYP, wd=0.1, clip=1.0, grad_scale=1.0, t=9)))
+    assert eng.status().error == 0
+    gp, ft, sc = to_host(eng.master), to_host(fp8_t), eng.scale_tensor().cpu().numpy()
+    for i, (r, c) in enumerate(shapes):
+        amax, scale, q = oracle.fp8_quant(gp[segs.slice_of(f"w{i}")])
+        assert np.float32(sc[i]) == np.float32(scale)
+        got = ft[aux[i].fp8_t_off:aux[i].fp8_t_off + r * c].reshape(c, r)
+        assert np.array_equal(got, q.reshape(r, c).T), (r, c)
+    eng.close()
