@@ -1365,12 +1365,24 @@ __global__ void __launch_bounds__(ANNI_THREADS) f32_to_bf16_kernel(uint16_t *dst
 
 /* y += a x (num/gpu.h:299 of the reference, gpu_mat_axpy). */
 __global__ void __launch_bounds__(ANNI_THREADS) axpy_kernel(float *y, const float *x, float a,
-	uint64_t n)
+	uint64_t n, int aligned)
 {
-	const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+	const uint64_t stride = (uint64_t)gridDim.x * ANNI_UCHUNK;
 
-	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-		y[i] = fmaf(a, x[i], y[i]);
+	for (uint64_t e = (uint64_t)blockIdx.x * ANNI_UCHUNK + (uint64_t)threadIdx.x * ANNI_UVEC; e < n;
+	    e += stride) {
+		if (aligned && e + ANNI_UVEC <= n) {
+			const f32x4 xv = io4<float>::load(x, e);
+			f32x4 yv = io4<float>::load(y, e);
+
+#pragma unroll
+			for (int k = 0; k < ANNI_UVEC; k++)
+				yv.x[k] = fmaf(a, xv.x[k], yv.x[k]);
+			io4<float>::store(y, e, yv);
+		} else
+			for (int k = 0; k < ANNI_UVEC && e + k < n; k++)
+				y[e + k] = fmaf(a, x[e + k], y[e + k]);
+	}
 }
 
 std::atomic<uint64_t> g_launches{0};
@@ -1640,7 +1652,8 @@ extern "C" int anni_launch_axpy(float *y, const float *x, float a, uint64_t n, c
 {
 	if (!y || !x || n == 0)
 		return ANNI_E_ARG;
-	axpy_kernel<<<flat_blocks(n), ANNI_THREADS, 0, st>>>(y, x, a, n);
+	axpy_kernel<<<flat_blocks(n), ANNI_THREADS, 0, st>>>(y, x, a, n,
+	    (((uintptr_t)y | (uintptr_t)x) & 15) == 0);
 	anni_count_launch();
 	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
