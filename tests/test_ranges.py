@@ -81,3 +81,25 @@ def test_reduce_norm_in_parts_accumulates_the_sum_of_squares():
     assert abs(out[0][1][0] - out[1][1][0]) <= 1e-14 * out[0][1][0]
     ref = float((to_host(src).astype(np.uint32) << 16).view(np.float32).astype(np.float64).__pow__(2).sum())
     assert abs(out[1][1][0] - ref) <= 1e-12 * ref
+
+
+@pytest.mark.parametrize("sc", [0, 1, 3])
+def test_other_super_chunk_sizes_give_the_same_bits(sc, monkeypatch):
+    """The tuning knob ANNI_B200_SUPERCHUNK moves chunks between blocks and switches the
+    per-super-chunk short cuts off or on; without clipping the result does not depend on it."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin="fp8")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=8, grad_dtype=DT_BF16, state_dtype=DT_BF16)
+    hp = OptStep.hyper(lr=3e-4, t=3, beta2=0.95, wd=0.1, clip=0.0, check_finite=True)
+    ref = _engine(segs, DT_BF16, DT_BF16, p, g, m, v)
+    ref.step(hp)
+    monkeypatch.setenv("ANNI_B200_SUPERCHUNK", str(sc))
+    for split in (False, True):
+        eng = _engine(segs, DT_BF16, DT_BF16, p, g, m, v)
+        (eng.step_split if split else eng.step)(hp)
+        assert eng.status().error == 0 and eng.status().skipped == 0
+        for name in ("master", "m", "v", "grad", "twin_bf16", "twin_fp8"):
+            assert torch.equal(getattr(ref, name), getattr(eng, name)), (name, split)
+        assert torch.equal(ref.scale_tensor(), eng.scale_tensor())
+        eng.close()
+    ref.close()
