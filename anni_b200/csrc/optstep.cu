@@ -3,25 +3,31 @@
 **
 ** The work is HBM-bound streaming arithmetic, so there are no tensor cores
 ** here.  What the design spends its effort on instead:
-**   - every HBM access of the main path is a 128-bit coalesced load or store
-**     with a streaming cache hint, eight elements per thread per chunk;
-**   - the grid is persistent (a multiple of the SM count, all blocks
-**     co-resident) and every block owns one contiguous run of chunks, walked
-**     forwards for the norm and backwards for the update so that the tail of
-**     the gradient shard is still in L2 when it is read the second time;
+**   - every HBM access of the main path is a coalesced vector load or store with a
+**     streaming cache hint: eight elements per thread per chunk in the norm phase, four
+**     in the update and quantise phases -- the geometry that keeps the loads queued per
+**     SM near the memory system's best point (about 36 KB; more is slower) while leaving
+**     enough warps to hide the arithmetic;
+**   - the grid is persistent (a multiple of the SM count, all blocks co-resident);
+**     chunks are dealt round-robin in super-chunks of four, so the whole grid works
+**     inside one contiguous window of every buffer; the norm walks forwards and the
+**     update backwards, so that the tail of the gradient shard is still in L2 when it
+**     is read the second time;
 **   - the global dependency (the gradient norm) is resolved on the device:
 **     fixed-order fp64 block partials, a bounded device-wide barrier, and every
 **     block derives the same clip factor / skip decision from the same bits;
-**   - tensor boundaries, the decay mask and the twin format are looked up from
-**     a replicated segment table per chunk, so one launch covers every tensor.
+**   - tensor boundaries, the decay mask and the twin format come from a replicated
+**     segment table, looked up once per super-chunk, so one launch covers every tensor.
 **
 ** Arithmetic (what "parity" is measured against): the moments are updated in
 ** double with the roundings of lang/lm_adam.c:587-591 of the reference
 ** (products and sum rounded separately, result stored as float), which makes
 ** m and v bit-identical to the reference's host loop whenever the gradient
-** multiplier is bit-identical.  The parameter update uses the float moments
-** with IEEE float division and square root; it stays within one ulp of the
-** reference's double expression for ordinary magnitudes.
+** multiplier is bit-identical.  The parameter update runs from the float moments,
+** either in float with the SFU's approximate square root and reciprocal (fast mode,
+** within an ulp or two of the reference's double expression for ordinary magnitudes)
+** or in double with Newton-refined SFU seeds (ANNI_STEP_EXACT_UPDATE, bit-identical
+** in all but about one element in 10^5).
 */
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>

@@ -14,11 +14,12 @@
 #define ANNI_CHUNK		(ANNI_THREADS * ANNI_VEC)
 #define ANNI_CHUNK_LOG2		11
 /*
-** Update and quantise phases: four elements per thread per chunk.  Measured on
-** B200 with the update's access mix (5 read and 6 write streams): HBM
-** throughput peaks when about 4096 elements per SM are in flight and drops
-** ~7 % at twice that, while the arithmetic wants 1024 threads per SM to hide
-** its latencies -- hence 4 blocks x 256 threads x 4 elements.
+** Update and quantise phases: four elements per thread per chunk.  Measured on B200 with
+** the update's access mix (4 read and 5 write streams, 22 bytes per element): HBM
+** throughput peaks with about 36 KB of loads queued per SM and drops 5-8 % with 48-72 KB,
+** while the arithmetic wants 1024 threads per SM to hide its latencies -- hence 4 blocks x
+** 256 threads x 4 elements for bf16 moments (12 bytes per element in flight), 3 blocks for
+** fp32 moments (14-16 bytes).
 */
 #define ANNI_UVEC		4
 #define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
