@@ -333,6 +333,8 @@ def run_ours(args):
     exact_ms = None
     if world == 1:
         refill()
+        torch.cuda.synchronize()
+        time.sleep(1.0)             # the refill runs at the power cap; let the clocks come back first
         k_ex = min(10, pool_n - 2)
         for i in range(2):
             bind_grads(pool[i])
@@ -349,6 +351,35 @@ def run_ours(args):
         e1.record()
         barrier()
         exact_ms = e0.elapsed_time(e1) / k_ex
+
+    # ---- the two phases apart (three-launch form), outside the timed region ------------------
+    split_ms = None
+    if world == 1:
+        refill()
+        torch.cuda.synchronize()
+        time.sleep(1.0)             # the refill runs at the power cap; let the clocks come back first
+        k_sp = min(10, pool_n - 2)
+        marks = []
+        for i in range(2 + k_sp):
+            bind_grads(pool[i])
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            hp_i = hyper(t)
+            evs[0].record()
+            z.eng.norm(hp_i)
+            evs[1].record()
+            z.eng.update(hp_i)
+            if z.eng.has_fp8:
+                z.eng.quantize()
+            evs[2].record()
+            t += 1
+            marks.append(evs)
+        barrier()
+        if os.environ.get("ANNI_BENCH_DEBUG"):
+            print("split per step:", [(round(a.elapsed_time(b), 3), round(b.elapsed_time(c), 3)) for a, b, c in marks],
+                  file=sys.stderr)
+        marks = marks[2:]
+        split_ms = {"norm": sum(a.elapsed_time(b) for a, b, _ in marks) / k_sp,
+                    "update": sum(b.elapsed_time(c) for _, b, c in marks) / k_sp}
 
     # ---- e2e: host gradient buffers through the C ABI --------------------------------------
     e2e_steps = max(2, min(5, K))
@@ -429,6 +460,10 @@ def run_ours(args):
         line["exact_update"] = {"ms_per_step": exact_ms, "value": n / (exact_ms * 1e-3),
                                 "roofline_frac": alg_bytes * n / (exact_ms * 1e-3) / 1e9 / peak,
                                 "note": "same step with ANNI_STEP_EXACT_UPDATE (update term in double)"}
+        line["phases_ms"] = dict(split_ms, note="three-launch form of the same step, timed apart: the norm pass "
+                                 "(a second read of the gradients) and the update pass; a caller whose "
+                                 "gradient producer supplies the sum of squares pays the update pass only")
+        line["phases_ms"]["update_only_roofline_frac"] = alg_bytes * n / (split_ms["update"] * 1e-3) / 1e9 / peak
         base, _ = cpu_reference_step_rate(64 * 1024 * 1024, 3, 1)
         line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)
