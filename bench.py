@@ -258,6 +258,8 @@ def run_ours(args):
     if sampler:
         sampler.start()
     refill()
+    torch.cuda.synchronize()
+    time.sleep(1.0)                 # filling the pool runs at the power cap; let the clocks come back
     t = 1000
     done = 0
     for _ in range(W):
@@ -279,6 +281,8 @@ def run_ours(args):
             batch = min(left, pool_n - (done % pool_n)) if done % pool_n else min(left, pool_n)
         if world == 1 and done % pool_n == 0 and done > 0:
             refill()
+            torch.cuda.synchronize()
+            time.sleep(1.0)
         barrier()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
