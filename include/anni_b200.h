@@ -131,7 +131,8 @@ typedef struct anni_optstep_status {
 /* ---- life cycle ---------------------------------------------------------- */
 
 /* Creates an engine on the current CUDA device (allocates its small control
-** block and device copies of the segment table). */
+** block and device copies of the segment table).  Every later call on the engine
+** must be made with that device current (one process per GPU: set it once). */
 int	anni_optstep_create(const anni_optstep_config *cfg, anni_optstep **out);
 void	anni_optstep_destroy(anni_optstep *h);
 int	anni_optstep_bind(anni_optstep *h, const anni_optstep_buffers *buf);
