@@ -84,6 +84,10 @@ def lib():
     L.anni_optstep_quantize_ex.argtypes = [vp, i, vp]
     L.anni_peer_copy.restype = i
     L.anni_peer_copy.argtypes = [vp, vp, C.c_size_t, vp]
+    L.anni_arena_alloc.restype = i
+    L.anni_arena_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.POINTER(C.c_size_t), C.POINTER(i)]
+    L.anni_arena_free.restype = i
+    L.anni_arena_free.argtypes = [vp, C.c_size_t]
     L.anni_optstep_selftest_barrier_timeout.restype = i
     L.anni_optstep_selftest_barrier_timeout.argtypes = [vp, C.c_uint, vp]
     L.anni_optstep_quantize.restype = i

@@ -158,7 +158,11 @@ static void release_device(anni_lm_adam *opt)
 	cudaFree(opt->d_param);
 	cudaFree(opt->d_param_bf16);
 	cudaFree(opt->d_param_fp8);
-	cudaFree(opt->d_grad);
+	if (opt->grad_arena_bytes)
+		(void)anni_arena_free(opt->d_grad, opt->grad_arena_bytes);
+	else
+		cudaFree(opt->d_grad);
+	opt->grad_arena_bytes = 0;
 	cudaFree(opt->d_m);
 	cudaFree(opt->d_v);
 	opt->d_param = NULL;
@@ -273,11 +277,22 @@ static int ensure_device(anni_lm_adam *opt)
 		for (i = 0; i < opt->n_segs; i++)
 			if (opt->segs[i].flags & ANNI_SEG_TWIN_FP8)
 				any_fp8 = 1;
+		/*
+		** The gradient flat goes into compressible memory where the device has it: every step
+		** leaves it zeroed, and zero lines then cost a fraction of their size on the way to HBM
+		** (about 4 % of the step at 555 M parameters).  Plain memory otherwise.
+		*/
+		if (anni_arena_alloc(n * elem_size(opt->grad_dtype), &opt->d_grad, &opt->grad_arena_bytes,
+		    NULL) != ANNI_OK) {
+			opt->d_grad = NULL;
+			opt->grad_arena_bytes = 0;
+			(void)cudaGetLastError();
+		}
 		if (cudaMalloc((void **)&opt->d_param, n * 4u) != cudaSuccess
-		    || cudaMalloc(&opt->d_grad, n * elem_size(opt->grad_dtype)) != cudaSuccess
+		    || (!opt->d_grad && (cudaMalloc(&opt->d_grad, n * elem_size(opt->grad_dtype)) != cudaSuccess
+		    || cudaMemset(opt->d_grad, 0, n * elem_size(opt->grad_dtype)) != cudaSuccess))
 		    || cudaMalloc(&opt->d_param_bf16, n * 2u) != cudaSuccess
 		    || (any_fp8 && cudaMalloc(&opt->d_param_fp8, n) != cudaSuccess)
-		    || cudaMemset(opt->d_grad, 0, n * elem_size(opt->grad_dtype)) != cudaSuccess
 		    || cudaMemset(opt->d_param_bf16, 0, n * 2u) != cudaSuccess
 		    || (any_fp8 && cudaMemset(opt->d_param_fp8, 0, n) != cudaSuccess)) {
 			(void)cudaGetLastError();

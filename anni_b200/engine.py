@@ -365,5 +365,41 @@ class OptStep:
             pass
 
 
+class CompressibleArena:
+    """A zeroed device buffer in compressible memory (anni_arena_alloc) seen as a torch tensor.
+    Meant for the gradient arena, which every step leaves zeroed: the L2 writes zero lines back
+    at a fraction of their size.  Raises capi.AnniError(E_LIMIT) where the device has no such
+    memory; keep the object alive as long as the tensor is in use."""
+
+    def __init__(self, n, dtype, device="cuda"):
+        self.L = capi.lib()
+        esz = torch.empty((), dtype=dtype).element_size()
+        p, size, comp = C.c_void_p(), C.c_size_t(), C.c_int()
+        with torch.cuda.device(torch.device(device)):
+            check("anni_arena_alloc", self.L.anni_arena_alloc(int(n) * esz, C.byref(p), C.byref(size),
+                                                              C.byref(comp)))
+        self.ptr, self.mapped_bytes, self.compressed = p, size.value, bool(comp.value)
+
+        class _Holder:
+            pass
+        hold = _Holder()
+        hold.__cuda_array_interface__ = {"shape": (int(n),), "typestr": {1: "|u1", 2: "<i2", 4: "<f4"}[esz],
+                                         "data": (int(p.value), False), "version": 3, "strides": None}
+        t = torch.as_tensor(hold, device=torch.device(device))
+        self.tensor = t if t.dtype == dtype else t.view(dtype)
+
+    def close(self):
+        if getattr(self, "ptr", None):
+            self.tensor = None
+            self.L.anni_arena_free(self.ptr, self.mapped_bytes)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def kernel_launches():
     return int(capi.lib().anni_kernel_launches())

@@ -112,6 +112,7 @@ class Zero1:
         self.eng = make_stepper(min(self.shard_off, self.n_arena), self.shard_n)
         gdt, sdt, dev = _TORCH_DT[grad_dtype], _TORCH_DT[state_dtype], self.device
         self._gdt = gdt
+        self._arenas = []
         if peer is None:
             peer = self.world > 1 and dev.type == "cuda" and hasattr(self.eng, "set_peers")
         self.copy_mode = peer == "copy" and self.world > 1
@@ -138,7 +139,7 @@ class Zero1:
                     self._parts = [(0, 0)]
             self._attach_peers()
         else:
-            self.grad_full = torch.zeros(self.padded, dtype=gdt, device=dev)
+            self.grad_full = self._local_grad_arena()
             self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
             self.twin8_full = (torch.zeros(self.padded, dtype=torch.uint8, device=dev)
                                if self.eng.has_fp8 else None)
@@ -183,11 +184,28 @@ class Zero1:
         if self.uses_multicast:
             self.eng.set_multicast(pg[1], pt[1], p8[1] if p8 else 0, off)
 
+    def _local_grad_arena(self):
+        """A zeroed gradient arena in this GPU's memory: compressible memory where the device has
+        it (every step leaves the arena zeroed, and zero lines then cost a fraction of their size
+        on the way to HBM), plain memory otherwise."""
+        if self.device.type == "cuda":
+            from . import capi
+            from .engine import CompressibleArena
+            try:
+                arena = CompressibleArena(self.padded, self._gdt, self.device)
+            except capi.AnniError as e:
+                if e.code != capi.E_LIMIT:
+                    raise
+            else:
+                self._arenas.append(arena)          # keeps the mapping alive as long as this object
+                return arena.tensor
+        return torch.zeros(self.padded, dtype=self._gdt, device=self.device)
+
     def new_grad_arena(self):
         """Another full gradient arena (e.g. one per micro-step buffer); see use_grad_arena."""
         if self.peer:
             return self._symm(self.padded, self._gdt)
-        return torch.zeros(self.padded, dtype=self._gdt, device=self.device), None
+        return self._local_grad_arena(), None
 
     def use_grad_arena(self, arena):
         """Make (tensor, peer pointers) from new_grad_arena the input of the next steps."""

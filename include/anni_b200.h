@@ -247,6 +247,18 @@ int	anni_peer_copy(void *dst, const void *src, size_t nbytes, void *stream);
 /* anni_optstep_quantize with ANNI_RANGE_LOCAL_TWINS: the e4m3 twins through the bound buffer only. */
 int	anni_optstep_quantize_ex(anni_optstep *h, int flags, void *stream);
 /*
+** Device memory with the GPU's memory compression switched on, for buffers whose contents
+** compress well: the gradient arena, which every step leaves zeroed.  The L2 then writes such
+** lines back to HBM at a fraction of their size.  No counterpart in the reference (its
+** optimizer allocates the flats with gpu_malloc); results do not depend on it.
+**   anni_arena_alloc   nbytes of zeroed memory on the current device; *mapped_bytes is what to
+**                      pass to anni_arena_free.  ANNI_E_LIMIT: the device or driver does not
+**                      offer compressible memory (nothing allocated: use cudaMalloc).
+**   anni_arena_free    synchronises the device, unmaps and releases.
+*/
+int	anni_arena_alloc(size_t nbytes, void **out, size_t *mapped_bytes, int *compressed);
+int	anni_arena_free(void *ptr, size_t mapped_bytes);
+/*
 ** Optional, after anni_optstep_set_peers: NVSwitch multicast addresses of the same three arenas
 ** (element 0 of the padded arena; NULL for any that has none).  The reduce kernel then issues one
 ** multimem.ld_reduce per vector (the switch adds all ranks' copies; bf16 accumulated in float) and

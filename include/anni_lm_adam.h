@@ -25,6 +25,7 @@
 #ifndef ANNI_LM_ADAM_H__
 #define ANNI_LM_ADAM_H__
 
+#include <stddef.h>
 #include <stdint.h>
 #include "anni_b200.h"
 #include "anni_gpu_compat.h"
@@ -86,6 +87,7 @@ typedef struct anni_lm_adam {
 	void		*snap_v;
 	void		*snap_stream;
 	void		*snap_event;
+	size_t		grad_arena_bytes;	/* > 0: d_grad is compressible memory of this mapped size (anni_arena_alloc) */
 	anni_optstep	*engine;
 } anni_lm_adam;
 

@@ -242,7 +242,7 @@ class LmAdam(C.Structure):
                 ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("last_skipped", C.c_int),
                 ("last_error", C.c_int), ("loss_scale", d), ("exact_update", C.c_int),
                 ("snap_m", C.c_void_p), ("snap_v", C.c_void_p), ("snap_stream", C.c_void_p),
-                ("snap_event", C.c_void_p), ("engine", C.c_void_p)]
+                ("snap_event", C.c_void_p), ("grad_arena_bytes", C.c_size_t), ("engine", C.c_void_p)]
 
 
 def _mirror():
