@@ -46,7 +46,7 @@ HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0)
 # DRAM bytes per parameter of the fused kernel from the ncu capture summarised in
 # profiles/fused_kernel_bf16state_100M.md (dram__bytes_read.sum + dram__bytes_write.sum of a
 # 100.7M-parameter launch; traffic grows in proportion to the parameter count).
-NCU_DRAM_BYTES_PER_PARAM = 22.95
+NCU_DRAM_BYTES_PER_PARAM = 21.54   # dram read + write of one fused launch / parameters (ncu, 100.7 M case, profiles/)
 
 
 def measured_peaks():
@@ -432,10 +432,12 @@ def run_ours(args):
                    "update_arithmetic": "double moments, float update (fast mode)",
                    "zero_grad": True, "zero1_ranks": world,
                    "l2": "inputs larger than L2 (6.7 GB state + a fresh 1.1 GB gradient arena per step)",
+                   "grad_arena": ("compressible device memory (anni_arena_alloc)" if getattr(z, "_arenas", None)
+                                  else "symmetric memory" if z.peer else "plain device memory"),
                    "hbm_gbs_alg": (alg_bytes * n / (ms_per_step * 1e-3) / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak if achieved else None,
-                     "traffic": NCU_DRAM_BYTES_PER_PARAM * shard_n if args.workload == WORKLOAD else None,
+                     "traffic": NCU_DRAM_BYTES_PER_PARAM * shard_n if args.workload == WORKLOAD and world == 1 else None,
                      "kernel": f"fused_kernel<{gdt_name},{sdt_name}>" if world == 1 else f"update_kernel<{gdt_name},{sdt_name}>",
                      "kernel_ms": kern_ms, "peak_kind": f"of {peak_kind}",
                      "frac_of_8000": achieved / 8000.0 if achieved else None},
