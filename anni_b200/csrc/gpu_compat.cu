@@ -21,6 +21,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <mutex>
+#include <unordered_map>
 #include "anni_gpu_compat.h"
 #include "optstep_internal.h"
 
@@ -39,6 +40,7 @@ void *g_flat_bf16;
 const float *g_flat_fp32;
 size_t g_flat_n;
 std::mutex g_malloc_lock;	/* gpu_malloc may be entered from worker threads (gpu_cuda.cu:2644) */
+std::unordered_map<void *, size_t> g_arena_blocks;	/* blocks handed out by anni_arena_alloc -> mapped size */
 
 /* device state of the two legacy optimizer calls, created on first use */
 struct legacy_state {
@@ -175,13 +177,29 @@ extern "C" void gpu_device_sync(void)
 		(void)cudaDeviceSynchronize();
 }
 
+/*
+** Large blocks (the optimizer's flats, lang/lm_adam.c:217-311) come from compressible memory
+** where the device has it: the gradient flat is left zeroed by every step, and zeroed lines
+** then cost a fraction of their size on the way to HBM.  Data that does not compress costs the
+** same as in plain memory.  Small blocks, and every block where compression is unavailable,
+** are plain cudaMalloc memory.  g_arena_blocks remembers which is which for gpu_free.
+*/
+#define ANNI_COMPRESSIBLE_FROM	((size_t)8 << 20)
+
 extern "C" void *gpu_malloc(size_t nbytes)
 {
 	void *p = NULL;
+	size_t mapped = 0;
 	std::lock_guard<std::mutex> hold(g_malloc_lock);
 
 	if (!gpu_available() || nbytes == 0)
 		return NULL;
+	if (nbytes >= ANNI_COMPRESSIBLE_FROM && anni_arena_alloc(nbytes, &p, &mapped, NULL) == ANNI_OK) {
+		g_arena_blocks[p] = mapped;
+		return p;
+	}
+	(void)cudaGetLastError();
+	p = NULL;
 	if (cudaMalloc(&p, nbytes) != cudaSuccess) {
 		(void)cudaGetLastError();
 		return NULL;
@@ -193,8 +211,15 @@ extern "C" void gpu_free(void *p)
 {
 	std::lock_guard<std::mutex> hold(g_malloc_lock);
 
-	if (p && gpu_available())
-		(void)cudaFree(p);
+	if (!p || !gpu_available())
+		return;
+	auto it = g_arena_blocks.find(p);
+	if (it != g_arena_blocks.end()) {
+		(void)anni_arena_free(p, it->second);
+		g_arena_blocks.erase(it);
+		return;
+	}
+	(void)cudaFree(p);
 }
 
 extern "C" int gpu_memcpy_h2d(void *dst, const void *src, size_t nbytes)

@@ -59,3 +59,33 @@ def test_step_on_a_compressible_gradient_arena_gives_the_same_bits(gd):
     for a, b in zip(outs[0][:5], outs[1][:5]):
         assert torch.equal(a, b)
     assert outs[0][5:] == outs[1][5:] and not outs[1][4].any()
+
+
+def test_large_gpu_malloc_blocks_are_compressible_and_behave():
+    """The reference-facing allocator (num/gpu.h:40-41): a large block comes from compressible
+    memory, works with the other gpu_* calls, and gpu_free knows how to release it."""
+    import ctypes as C
+    L = capi.lib()
+    L.gpu_malloc.restype = C.c_void_p
+    L.gpu_malloc.argtypes = [C.c_size_t]
+    L.gpu_free.argtypes = [C.c_void_p]
+    L.gpu_memcpy_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    L.gpu_grad_sumsq.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_double)]
+    L.gpu_mem_info.argtypes = [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+    assert L.gpu_available() == 1
+    n = 8 * 1024 * 1024                                    # 32 MB of floats: above the threshold
+    free0, tot = C.c_size_t(), C.c_size_t()
+    L.gpu_mem_info(C.byref(free0), C.byref(tot))
+    big, small = L.gpu_malloc(4 * n), L.gpu_malloc(4096)
+    assert big and small
+    host = np.random.default_rng(0).normal(0, 1e-3, n).astype(np.float32)
+    assert L.gpu_memcpy_h2d(big, host.ctypes.data, host.nbytes) == 0
+    ss = C.c_double()
+    assert L.gpu_grad_sumsq(big, n, C.byref(ss)) == 0
+    want = float((host.astype(np.float64) ** 2).sum())
+    assert abs(ss.value - want) <= 1e-12 * want
+    L.gpu_free(big)
+    L.gpu_free(small)
+    free1 = C.c_size_t()
+    L.gpu_mem_info(C.byref(free1), C.byref(tot))
+    assert free1.value >= free0.value - (4 << 20)          # the block went back
