@@ -122,3 +122,20 @@ def test_bad_arguments_are_refused_before_any_launch():
     big.n_seg = capi.NOALLOC_MAX_SEG + 1
     assert L.anni_optstep_step_noalloc(C.byref(big), C.byref(capi.Buffers()), C.byref(capi.Hyper()),
                                        None, None) == capi.E_LIMIT
+
+
+def test_part_wise_calls_and_helpers_refuse_bad_arguments():
+    L = capi.lib()
+    hp = capi.Hyper()
+    assert L.anni_optstep_update_range(None, C.byref(hp), 0, 0, 0, None) == capi.E_ARG
+    assert L.anni_optstep_reduce_norm_range(None, C.byref(hp), 0, 0, 0, None) == capi.E_ARG
+    assert L.anni_optstep_quantize_ex(None, 0, None) == capi.E_ARG
+    assert L.anni_peer_copy(None, None, 16, None) == capi.E_ARG
+    p, size, comp = C.c_void_p(), C.c_size_t(), C.c_int()
+    assert L.anni_arena_alloc(0, C.byref(p), C.byref(size), C.byref(comp)) == capi.E_ARG
+    assert L.anni_arena_alloc(1 << 20, None, C.byref(size), None) == capi.E_ARG
+    assert L.anni_arena_free(None, 0) == capi.OK
+    import torch
+    if not torch.cuda.is_available():                       # without a device the allocator says so
+        assert L.anni_arena_alloc(1 << 20, C.byref(p), C.byref(size), C.byref(comp)) in (capi.E_CUDA, capi.E_LIMIT)
+        assert not p.value and size.value == 0
