@@ -255,6 +255,8 @@ int	anni_optstep_quantize_ex(anni_optstep *h, int flags, void *stream);
 **                      pass to anni_arena_free.  ANNI_E_LIMIT: the device or driver does not
 **                      offer compressible memory (nothing allocated: use cudaMalloc).
 **   anni_arena_free    synchronises the device, unmaps and releases.
+** The memory comes from the driver's virtual-memory interface: release it with anni_arena_free
+** only (never cudaFree), and do not expect cudaIpcGetMemHandle to export it.
 */
 int	anni_arena_alloc(size_t nbytes, void **out, size_t *mapped_bytes, int *compressed);
 int	anni_arena_free(void *ptr, size_t mapped_bytes);
