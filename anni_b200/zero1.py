@@ -185,10 +185,10 @@ class Zero1:
             self.eng.set_multicast(pg[1], pt[1], p8[1] if p8 else 0, off)
 
     def _local_grad_arena(self):
-        """A zeroed gradient arena in this GPU's memory: compressible memory where the device has
-        it (every step leaves the arena zeroed, and zero lines then cost a fraction of their size
-        on the way to HBM), plain memory otherwise."""
-        if self.device.type == "cuda":
+        """A zeroed gradient arena in this GPU's memory: on one GPU compressible memory where the
+        device has it (every step leaves the arena zeroed, and zero lines then cost a fraction of
+        their size on the way to HBM), plain memory otherwise."""
+        if self.device.type == "cuda" and self.world == 1:      # several ranks: NCCL reads this arena; plain memory
             from . import capi
             from .engine import CompressibleArena
             try:
