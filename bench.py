@@ -106,6 +106,41 @@ class ClockSampler(threading.Thread):
 # reference arm: the reference's own CPU step (oracle/_ref), bounded sample
 # ----------------------------------------------------------------------------------------
 
+def cpu_reference_all_cores(ref, p, gsrc, steps):
+    """What every host core together can do with the reference's loop: one independent
+    reference optimizer per core, each over its own slice of the sample, stepped at the same
+    time (the loop itself is single-threaded; each slice clips by its own norm, which costs
+    the same arithmetic).  An upper bound for a parallelised reference, reported beside the
+    single-thread figure, not instead of it."""
+    import numpy as np
+    threads = max(1, os.cpu_count() or 1)
+    per = len(p) // threads
+    g = gsrc.copy()
+    handles = []
+    for k in range(threads):
+        sl = slice(k * per, (k + 1) * per)
+        ps, gs = p[sl], g[sl]
+        handles.append(ref.L.ref_adam_bench_create(ps.ctypes.data, gs.ctypes.data, per, HYPER["beta1"],
+                                                   HYPER["beta2"], HYPER["eps"], HYPER["wd"], HYPER["clip"], 999))
+    assert all(handles)
+    times = []
+    for i in range(1 + max(1, steps)):
+        g[:] = gsrc
+        ts = [threading.Thread(target=ref.L.ref_adam_bench_step, args=(h, HYPER["lr"], 1.0)) for h in handles]
+        t0 = time.perf_counter()
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        if i >= 1:
+            times.append(time.perf_counter() - t0)
+    for h in handles:
+        ref.L.ref_adam_bench_free(h)
+    sec = sum(times) / len(times)
+    return dict(value=per * threads / sec, threads=threads,
+                note="one independent reference optimizer per host core, stepped concurrently")
+
+
 def cpu_reference_step_rate(sample, steps, warmup):
     """params/s of lm_adam_step_scaled's host loop (the reference's object code when
     oracle/_ref/libannref.so exists, else this repository's C port), one thread."""
@@ -145,7 +180,10 @@ def cpu_reference_step_rate(sample, steps, warmup):
             if i >= warmup:
                 times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
-    return dict(value=sample / sec, unit="params/s", cores=cores, kind=kind,
+    extra = {}
+    if kind == "reference":
+        extra["all_cores"] = cpu_reference_all_cores(ref, p, gsrc, steps)
+    return dict(value=sample / sec, unit="params/s", cores=cores, kind=kind, **extra,
                 sample=f"{sample} fp32 parameters of the {WORKLOAD} distribution, {len(times)} timed "
                        f"steps of {sec * 1e3:.0f} ms, clip active, wd {HYPER['wd']}"), sec
 
