@@ -416,9 +416,6 @@ def run_ours(args):
             t += 1
             marks.append(evs)
         barrier()
-        if os.environ.get("ANNI_BENCH_DEBUG"):
-            print("split per step:", [(round(a.elapsed_time(b), 3), round(b.elapsed_time(c), 3)) for a, b, c in marks],
-                  file=sys.stderr)
         marks = marks[2:]
         split_ms = {"norm": sum(a.elapsed_time(b) for a, b, _ in marks) / k_sp,
                     "update": sum(b.elapsed_time(c) for _, b, c in marks) / k_sp}
