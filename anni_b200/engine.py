@@ -315,15 +315,12 @@ class OptStep:
     # -- small device buffers as tensors (for collectives) -----------------------------------
     def _as_tensor(self, ptr, n, dtype):
         """A torch view of library-owned device memory (no copy, not owned by torch)."""
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
-
         class _Holder:
             pass
         hold = _Holder()
         hold.__cuda_array_interface__ = {
             "shape": (n,), "typestr": {torch.float64: "<f8", torch.float32: "<f4"}[dtype],
             "data": (int(ptr), False), "version": 3, "strides": None}
-        del nbytes
         return torch.as_tensor(hold, device=self.device)
 
     def reduce_tensor(self):
