@@ -53,6 +53,8 @@ void	gpu_set_fp8(int on);					/* gpu.h:30 */
 void	gpu_set_fp8_dgrad(int on);				/* gpu.h:31 */
 int	gpu_fp8(void);						/* gpu.h:32 */
 void	gpu_device_sync(void);					/* gpu.h:38 */
+/* Blocks of 8 MB and more are compressible device memory where the GPU offers it (anni_arena_alloc
+** in anni_b200.h): same contents and behaviour, but release them with gpu_free, never cudaFree. */
 void	*gpu_malloc(size_t nbytes);				/* gpu.h:40 */
 void	gpu_free(void *p);					/* gpu.h:41 */
 int	gpu_memcpy_h2d(void *dst, const void *src, size_t nbytes);	/* gpu.h:42 */
