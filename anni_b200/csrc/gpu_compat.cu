@@ -420,7 +420,7 @@ extern "C" int anni_adam_step_dev64(ann_real_t *d_p, void *d_p_bf16, ann_real_t 
 	hp.grad_clip = 0.0;		/* the caller folded its clip factor into grad_scale */
 	hp.grad_scale = grad_scale;
 	hp.t = t;
-	/* "d_grad is zeroed after" (gpu.h:125-127); with fp32 moments the double update term is free */
+	/* "d_grad is zeroed after" (gpu.h:125-127); with fp32 moments the double update term costs a few per cent */
 	hp.flags = ANNI_STEP_ZERO_GRAD | ANNI_STEP_EXACT_UPDATE;
 	if (anni_fill_hyper(&la, &hp) != ANNI_OK)
 		return -1;		/* bias correction not positive, as gpu_cuda.cu:8681 */
