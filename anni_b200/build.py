@@ -12,9 +12,9 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libanni_b200.so")
 SOURCES = ["optstep.cu", "optstep_api.cu", "gpu_compat.cu", "lm_adam_b200.cu", "lm_checkpoint.cu",
-           "noalloc.cu", "arena_alloc.cu"]
+           "noalloc.cu", "arena_alloc.cu", "zero1.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared"]
+              "-Xcompiler", "-fPIC", "-shared", "-ldl"]
 
 
 def _nvcc():

@@ -46,6 +46,20 @@ class Status(C.Structure):
                 ("good_steps", C.c_int32), ("steps_done", C.c_int32)]
 
 
+class Zero1Config(C.Structure):
+    """anni_zero1_config (include/anni_zero1.h)."""
+    _fields_ = [("n_arena", C.c_uint64), ("grad_dtype", C.c_int), ("state_dtype", C.c_int),
+                ("n_seg", C.c_int), ("seg_off", C.c_void_p), ("seg_flags", C.c_void_p),
+                ("rank", C.c_int), ("world", C.c_int), ("nccl_comm", C.c_void_p),
+                ("grad_arena", C.c_void_p), ("twin_arena", C.c_void_p), ("twin_fp8_arena", C.c_void_p),
+                ("peer_grad", C.c_void_p), ("peer_twin", C.c_void_p), ("peer_twin_fp8", C.c_void_p),
+                ("mc_grad", C.c_void_p), ("mc_twin", C.c_void_p), ("mc_twin_fp8", C.c_void_p)]
+
+
+ZERO1_GRADS_COMPLETE = 1
+ZERO1_UNIQUE_ID_BYTES = 128
+
+
 def lib():
     """The loaded library (built on first use when nvcc is available)."""
     global _LIB
@@ -68,12 +82,18 @@ def lib():
         f = getattr(L, name)
         f.restype = i
         f.argtypes = [vp, C.POINTER(Hyper), vp]
+    L.anni_optstep_step_with_sumsq.restype = i
+    L.anni_optstep_step_with_sumsq.argtypes = [vp, C.POINTER(Hyper), vp, vp]
     L.anni_optstep_set_derived.restype = i
     L.anni_optstep_set_derived.argtypes = [vp, vp, vp, vp]
     L.anni_optstep_set_peers.restype = i
     L.anni_optstep_set_peers.argtypes = [vp, vp, vp, vp, i, C.c_uint64]
     L.anni_optstep_set_multicast.restype = i
     L.anni_optstep_set_multicast.argtypes = [vp, vp, vp, vp, C.c_uint64]
+    L.anni_optstep_rotate_peers.restype = i
+    L.anni_optstep_rotate_peers.argtypes = [vp, i]
+    L.anni_optstep_set_grad_arena.restype = i
+    L.anni_optstep_set_grad_arena.argtypes = [vp, vp, C.c_uint64, i]
     L.anni_optstep_reduce_norm.restype = i
     L.anni_optstep_reduce_norm.argtypes = [vp, C.POINTER(Hyper), vp]
     L.anni_optstep_reduce_norm_range.restype = i
@@ -107,6 +127,27 @@ def lib():
     L.anni_optstep_step_noalloc.argtypes = [C.POINTER(Config), C.POINTER(Buffers), C.POINTER(Hyper), vp, vp]
     L.anni_optstep_status_noalloc.restype = i
     L.anni_optstep_status_noalloc.argtypes = [C.POINTER(Status), vp]
+    L.anni_zero1_geometry.restype = i
+    L.anni_zero1_geometry.argtypes = [C.c_uint64, i, i] + [C.POINTER(C.c_uint64)] * 3
+    L.anni_zero1_nccl_available.restype = i
+    L.anni_zero1_unique_id.restype = i
+    L.anni_zero1_unique_id.argtypes = [vp]
+    L.anni_zero1_comm_init.restype = i
+    L.anni_zero1_comm_init.argtypes = [vp, i, i, C.POINTER(vp)]
+    L.anni_zero1_comm_free.restype = None
+    L.anni_zero1_comm_free.argtypes = [vp]
+    L.anni_zero1_create.restype = i
+    L.anni_zero1_create.argtypes = [C.POINTER(Zero1Config), C.POINTER(vp)]
+    L.anni_zero1_bind.restype = i
+    L.anni_zero1_bind.argtypes = [vp, vp, vp, vp, vp]
+    L.anni_zero1_set_grad_arena.restype = i
+    L.anni_zero1_set_grad_arena.argtypes = [vp, vp, vp, vp]
+    L.anni_zero1_step.restype = i
+    L.anni_zero1_step.argtypes = [vp, C.POINTER(Hyper), i, vp, vp]
+    L.anni_zero1_engine.restype = vp
+    L.anni_zero1_engine.argtypes = [vp]
+    L.anni_zero1_destroy.restype = None
+    L.anni_zero1_destroy.argtypes = [vp]
     L.anni_kernel_launches.restype = C.c_uint64
     L.anni_kernel_launches.argtypes = []
     _LIB = L

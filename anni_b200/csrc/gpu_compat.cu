@@ -178,13 +178,28 @@ extern "C" void gpu_device_sync(void)
 }
 
 /*
-** Large blocks (the optimizer's flats, lang/lm_adam.c:217-311) come from compressible memory
-** where the device has it: the gradient flat is left zeroed by every step, and zeroed lines
-** then cost a fraction of their size on the way to HBM.  Data that does not compress costs the
-** same as in plain memory.  Small blocks, and every block where compression is unavailable,
-** are plain cudaMalloc memory.  g_arena_blocks remembers which is which for gpu_free.
+** Plain cudaMalloc memory, as in the reference (neither zeroed nor synchronised).  The one
+** buffer that gains from compressible memory is the optimizer's gradient flat (every step
+** leaves it zeroed, and zeroed lines then cost a fraction of their size on the way to HBM);
+** the optimizer object of this library allocates that flat with anni_arena_alloc itself.  A
+** trainer that keeps the reference's own lm_adam.c, whose flats all come from here, can opt
+** in with ANNI_B200_COMPRESSIBLE_MALLOC=1: blocks of 8 MB and more then come from compressible
+** memory where the device has it (zeroed, mapped for this device only: not for IPC or peer
+** access).  g_arena_blocks remembers which blocks those are for gpu_free.
 */
 #define ANNI_COMPRESSIBLE_FROM	((size_t)8 << 20)
+
+static int compressible_malloc_on(void)
+{
+	static int on = -1;
+
+	if (on < 0) {
+		const char *e = getenv("ANNI_B200_COMPRESSIBLE_MALLOC");
+
+		on = (e && e[0] == '1') ? 1 : 0;
+	}
+	return on;
+}
 
 extern "C" void *gpu_malloc(size_t nbytes)
 {
@@ -194,7 +209,8 @@ extern "C" void *gpu_malloc(size_t nbytes)
 
 	if (!gpu_available() || nbytes == 0)
 		return NULL;
-	if (nbytes >= ANNI_COMPRESSIBLE_FROM && anni_arena_alloc(nbytes, &p, &mapped, NULL) == ANNI_OK) {
+	if (compressible_malloc_on() && nbytes >= ANNI_COMPRESSIBLE_FROM
+	    && anni_arena_alloc(nbytes, &p, &mapped, NULL) == ANNI_OK) {
 		g_arena_blocks[p] = mapped;
 		return p;
 	}
@@ -209,17 +225,24 @@ extern "C" void *gpu_malloc(size_t nbytes)
 
 extern "C" void gpu_free(void *p)
 {
-	std::lock_guard<std::mutex> hold(g_malloc_lock);
+	size_t mapped = 0;
 
 	if (!p || !gpu_available())
 		return;
-	auto it = g_arena_blocks.find(p);
-	if (it != g_arena_blocks.end()) {
-		(void)anni_arena_free(p, it->second);
-		g_arena_blocks.erase(it);
-		return;
+	{
+		std::lock_guard<std::mutex> hold(g_malloc_lock);
+		auto it = g_arena_blocks.find(p);
+
+		if (it != g_arena_blocks.end()) {
+			mapped = it->second;
+			g_arena_blocks.erase(it);
+		}
 	}
-	(void)cudaFree(p);
+	/* the release may wait for the device: not while other threads queue for the lock */
+	if (mapped)
+		(void)anni_arena_free(p, mapped);
+	else
+		(void)cudaFree(p);
 }
 
 extern "C" int gpu_memcpy_h2d(void *dst, const void *src, size_t nbytes)
@@ -303,18 +326,144 @@ extern "C" const char *gpu_debug_last_error(void)
 	return e == cudaSuccess ? "" : cudaGetErrorString(e);
 }
 
-extern "C" void gpu_op_prof_dump(void)
-{
-	static int on = -1;
+/*
+** ANN_OP_PROF=1 (num/gpu_cuda.cu:3205-3352, 3381-3409 of the reference): device time per kind
+** of operation from pairs of events recorded around each entry point of this library that
+** launches work for the optimizer; the pairs are resolved, and the table printed and reset,
+** by gpu_op_prof_dump, which the trainer calls once per optimizer step.
+*/
+namespace {
 
-	if (on < 0) {
+const char *const g_op_name[ANNI_OP_N] = { "adam", "sumsq", "colsum", "axpy", "convert" };
+struct op_pair {
+	int		op;
+	cudaEvent_t	e0;
+	cudaEvent_t	e1;
+};
+#define OP_SLOTS	1024
+op_pair g_op_ev[OP_SLOTS];
+int g_op_ev_made;
+int g_op_ev_n;
+double g_op_ms[ANNI_OP_N];
+long g_op_calls[ANNI_OP_N];
+int g_op_prof = -1;
+std::mutex g_op_lock;
+
+int op_prof_on(void)
+{
+	if (g_op_prof < 0) {
 		const char *e = getenv("ANN_OP_PROF");
 
-		on = (e && e[0] == '1') ? 1 : 0;
+		g_op_prof = (e && e[0] == '1') ? 1 : 0;
 	}
-	if (on)
-		fprintf(stderr, "[anni_b200] kernel launches so far: %llu\n",
-		    (unsigned long long)anni_kernel_launches());
+	return g_op_prof;
+}
+
+void op_prof_resolve(void)
+{
+	for (int i = 0; i < g_op_ev_n; i++) {
+		float ms = 0.0f;
+
+		if (cudaEventElapsedTime(&ms, g_op_ev[i].e0, g_op_ev[i].e1) == cudaSuccess) {
+			g_op_ms[g_op_ev[i].op] += ms;
+			g_op_calls[g_op_ev[i].op]++;
+		} else
+			(void)cudaGetLastError();
+	}
+	g_op_ev_n = 0;
+}
+
+}	/* namespace */
+
+extern "C" int anni_op_begin(int op, void *stream)
+{
+	std::lock_guard<std::mutex> hold(g_op_lock);
+	int i;
+
+	if (!op_prof_on() || op < 0 || op >= ANNI_OP_N)
+		return -1;
+	if (g_op_ev_n >= OP_SLOTS) {
+		/* the table is full (nobody dumped for a long while): fold what is finished */
+		if (cudaDeviceSynchronize() != cudaSuccess)
+			return -1;
+		op_prof_resolve();
+	}
+	i = g_op_ev_n;
+	if (i >= g_op_ev_made) {
+		if (cudaEventCreate(&g_op_ev[i].e0) != cudaSuccess || cudaEventCreate(&g_op_ev[i].e1) != cudaSuccess) {
+			(void)cudaGetLastError();
+			return -1;
+		}
+		g_op_ev_made = i + 1;
+	}
+	g_op_ev[i].op = op;
+	if (cudaEventRecord(g_op_ev[i].e0, (cudaStream_t)stream) != cudaSuccess) {
+		(void)cudaGetLastError();
+		return -1;
+	}
+	g_op_ev_n = i + 1;
+	return i;
+}
+
+extern "C" void anni_op_end(int slot, void *stream)
+{
+	std::lock_guard<std::mutex> hold(g_op_lock);
+
+	if (slot < 0 || slot >= g_op_ev_n)
+		return;
+	if (cudaEventRecord(g_op_ev[slot].e1, (cudaStream_t)stream) != cudaSuccess)
+		(void)cudaGetLastError();
+}
+
+extern "C" void anni_op_prof_enable(int on)
+{
+	std::lock_guard<std::mutex> hold(g_op_lock);
+
+	g_op_prof = on ? 1 : 0;
+}
+
+extern "C" int anni_op_prof_totals(const char *name, double *ms, long *calls)
+{
+	std::lock_guard<std::mutex> hold(g_op_lock);
+
+	if (!name || !gpu_available())
+		return -1;
+	if (cudaDeviceSynchronize() != cudaSuccess)
+		return -1;
+	op_prof_resolve();
+	for (int i = 0; i < ANNI_OP_N; i++)
+		if (strcmp(name, g_op_name[i]) == 0) {
+			if (ms)
+				*ms = g_op_ms[i];
+			if (calls)
+				*calls = g_op_calls[i];
+			return 0;
+		}
+	return -1;
+}
+
+extern "C" void gpu_op_prof_dump(void)
+{
+	std::lock_guard<std::mutex> hold(g_op_lock);
+	double tot = 0.0;
+
+	if (!op_prof_on() || !gpu_available())
+		return;
+	if (cudaDeviceSynchronize() == cudaSuccess)
+		op_prof_resolve();
+	for (int i = 0; i < ANNI_OP_N; i++)
+		tot += g_op_ms[i];
+	fprintf(stderr, "[opprof] %.3f ms of GPU op time in the optimizer's entry points, %llu kernel launches so far\n",
+	    tot, (unsigned long long)anni_kernel_launches());
+	for (int i = 0; i < ANNI_OP_N; i++) {
+		if (g_op_calls[i] == 0)
+			continue;
+		fprintf(stderr, "[opprof]   %-11s %8.3f ms %5.1f%% %6ld calls %8.3f ms/call\n", g_op_name[i],
+		    g_op_ms[i], tot > 0.0 ? 100.0 * g_op_ms[i] / tot : 0.0, g_op_calls[i],
+		    g_op_ms[i] / (double)g_op_calls[i]);
+		g_op_ms[i] = 0.0;
+		g_op_calls[i] = 0;
+	}
 }
 
 /* ---- the flat bf16 twin registry ---------------------------------------------- */
@@ -341,7 +490,13 @@ extern "C" int gpu_adam_seed_bf16_flat(void *bf16, const ann_real_t *fp32, int n
 {
 	if (!bf16 || !fp32 || n <= 0 || !gpu_available())
 		return -1;
-	return anni_launch_f32_to_bf16((uint16_t *)bf16, fp32, (uint64_t)n, g_st) == ANNI_OK ? 0 : -1;
+	{
+		const int slot = anni_op_begin(ANNI_OP_CONVERT, g_st);
+		const int rc = anni_launch_f32_to_bf16((uint16_t *)bf16, fp32, (uint64_t)n, g_st);
+
+		anni_op_end(slot, g_st);
+		return rc == ANNI_OK ? 0 : -1;
+	}
 }
 
 extern "C" void *anni_half_wt_lookup(const ann_real_t *fp32_dev, size_t n)
@@ -374,8 +529,14 @@ extern "C" int anni_grad_sumsq64(const void *d_x, int dtype, unsigned long long 
 	legacy_launch_base(&la, n);
 	la.grad = (void *)d_x;
 	la.aligned = ((uintptr_t)d_x & 15) == 0;
-	if (anni_launch_norm(&la, dtype, ANNI_DT_F32, g_legacy.blocks, g_st) != ANNI_OK)
-		return -1;
+	{
+		const int slot = anni_op_begin(ANNI_OP_SUMSQ, g_st);
+		const int rc = anni_launch_norm(&la, dtype, ANNI_DT_F32, g_legacy.blocks, g_st);
+
+		anni_op_end(slot, g_st);
+		if (rc != ANNI_OK)
+			return -1;
+	}
 	/* the reference returns the sum to the host with a blocking copy (gpu_cuda.cu:8532) */
 	if (cudaMemcpyAsync(out, (char *)g_legacy.ctl + offsetof(anni_control, reduce), sizeof(double),
 	    cudaMemcpyDeviceToHost, g_st) != cudaSuccess)
@@ -425,8 +586,13 @@ extern "C" int anni_adam_step_dev64(ann_real_t *d_p, void *d_p_bf16, ann_real_t 
 	if (anni_fill_hyper(&la, &hp) != ANNI_OK)
 		return -1;		/* bias correction not positive, as gpu_cuda.cu:8681 */
 	la.flags |= ANNI_LAUNCH_HOST_COEF;
-	return anni_launch_update(&la, ANNI_DT_F32, ANNI_DT_F32, g_legacy.blocks, g_st) == ANNI_OK
-	    ? 0 : -1;
+	{
+		const int slot = anni_op_begin(ANNI_OP_ADAM, g_st);
+		const int rc = anni_launch_update(&la, ANNI_DT_F32, ANNI_DT_F32, g_legacy.blocks, g_st);
+
+		anni_op_end(slot, g_st);
+		return rc == ANNI_OK ? 0 : -1;
+	}
 }
 
 extern "C" int gpu_adam_step_dev_bf16(ann_real_t *d_p, void *d_p_bf16, ann_real_t *d_g,
@@ -470,10 +636,130 @@ extern "C" int gpu_mat_axpy(anni_mat *y, double a, const anni_mat *x)
 			mt->on_device = 2;
 		}
 	}
-	if (anni_launch_axpy(y->d_data, x->d_data, (float)a, n, g_st) != ANNI_OK)
-		return -1;
+	{
+		const int slot = anni_op_begin(ANNI_OP_AXPY, g_st);
+		const int rc = anni_launch_axpy(y->d_data, x->d_data, (float)a, n, g_st);
+
+		anni_op_end(slot, g_st);
+		if (rc != ANNI_OK)
+			return -1;
+	}
 	if (y->on_device != 3)
 		y->on_device = 1;	/* device-authoritative; an aliased view stays aliased */
+	if (g_sync_mode_v == ANNI_GPU_SYNC_EAGER)
+		(void)cudaStreamSynchronize(g_st);
+	return 0;
+}
+
+/* ---- bias / LayerNorm gradients that never leave the device -------------------------- */
+
+/*
+** The reference accumulates the column sums that make a bias gradient in a device buffer keyed
+** by the HOST gradient vector and adds them into that vector at the next device sync
+** (colsum_acc, num/gpu_cuda.cu:3130-3195), from where the optimizer uploads them again each
+** step (seg_gather, lang/lm_adam.c:361-396).  Here the optimizer object registers, per vector
+** tensor, the slice of its device gradient flat that stands for the host vector
+** (anni_lm_adam_alias_vec): gpu_mat_col_sum_add then adds straight into the flat and the
+** gradient never travels.  Unregistered vectors answer -1, "use the CPU path", as before.
+*/
+namespace {
+
+struct colsum_slot {
+	const ann_real_t	*host;
+	float			*dev;
+	int			cols;
+};
+#define COLSUM_SLOTS	1024
+colsum_slot g_colsum[COLSUM_SLOTS];
+int g_colsum_n;
+std::mutex g_colsum_lock;
+
+/* out[c] += sum over rows of x[r][c]: one block per 32 columns, eight row lanes, fixed order */
+__global__ void __launch_bounds__(256) colsum_add_kernel(float *out, const float *x, int rows, int cols)
+{
+	__shared__ float part[8][33];
+	const int lane = threadIdx.x & 31;
+	const int rg = threadIdx.x >> 5;
+	const int c = blockIdx.x * 32 + lane;
+	float acc = 0.0f;
+
+	if (c < cols)
+		for (int r = rg; r < rows; r += 8)
+			acc += x[(size_t)r * cols + c];
+	part[rg][lane] = acc;
+	__syncthreads();
+	if (rg == 0 && c < cols) {
+		float t = part[0][lane];
+
+		for (int k = 1; k < 8; k++)
+			t += part[k][lane];
+		out[c] += t;
+	}
+}
+
+}	/* namespace */
+
+extern "C" int anni_colsum_register(const ann_real_t *host, float *dev, int cols)
+{
+	std::lock_guard<std::mutex> hold(g_colsum_lock);
+
+	if (!host || !dev || cols <= 0)
+		return -1;
+	for (int i = 0; i < g_colsum_n; i++)
+		if (g_colsum[i].host == host) {
+			g_colsum[i].dev = dev;
+			g_colsum[i].cols = cols;
+			return 0;
+		}
+	if (g_colsum_n >= COLSUM_SLOTS)
+		return -1;
+	g_colsum[g_colsum_n].host = host;
+	g_colsum[g_colsum_n].dev = dev;
+	g_colsum[g_colsum_n].cols = cols;
+	g_colsum_n++;
+	return 0;
+}
+
+extern "C" void anni_colsum_forget(const void *dev_lo, const void *dev_hi)
+{
+	std::lock_guard<std::mutex> hold(g_colsum_lock);
+	int k = 0;
+
+	for (int i = 0; i < g_colsum_n; i++)
+		if ((const void *)g_colsum[i].dev < dev_lo || (const void *)g_colsum[i].dev >= dev_hi)
+			g_colsum[k++] = g_colsum[i];
+	g_colsum_n = k;
+}
+
+extern "C" int gpu_mat_col_sum_add(ann_real_t *db_host, const ann_real_t *x, int rows, int cols)	/* gpu.h:198 */
+{
+	cudaPointerAttributes at;
+	float *dev = NULL;
+
+	if (!db_host || !x || rows <= 0 || cols <= 0 || !gpu_available())
+		return -1;
+	{
+		std::lock_guard<std::mutex> hold(g_colsum_lock);
+
+		for (int i = 0; i < g_colsum_n; i++)
+			if (g_colsum[i].host == db_host && g_colsum[i].cols == cols)
+				dev = g_colsum[i].dev;
+	}
+	if (!dev)
+		return -1;	/* not a registered gradient vector: the caller's CPU path */
+	if (cudaPointerGetAttributes(&at, x) != cudaSuccess || at.type != cudaMemoryTypeDevice) {
+		(void)cudaGetLastError();
+		return -1;	/* the matrix must already be on the device */
+	}
+	{
+		const int slot = anni_op_begin(ANNI_OP_COLSUM, g_st);
+
+		colsum_add_kernel<<<(cols + 31) / 32, 256, 0, g_st>>>(dev, x, rows, cols);
+		anni_count_launch();
+		anni_op_end(slot, g_st);
+	}
+	if (cudaGetLastError() != cudaSuccess)
+		return -1;
 	if (g_sync_mode_v == ANNI_GPU_SYNC_EAGER)
 		(void)cudaStreamSynchronize(g_st);
 	return 0;
@@ -516,7 +802,6 @@ ANSWERS_ZERO(gpu_ce_bias_fused)
 NOT_ON_DEVICE(gpu_ce_bf16_delta_done)
 NOT_ON_DEVICE(gpu_ce_nll_rows)
 NOT_ON_DEVICE(gpu_posenc_add_packed)
-NOT_ON_DEVICE(gpu_mat_col_sum_add)
 NOT_ON_DEVICE(gpu_relu_backward)
 NOT_ON_DEVICE(gpu_ffn_relu_bwd_fused)
 ANSWERS_ZERO(gpu_act_bf16_only)

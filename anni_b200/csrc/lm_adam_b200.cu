@@ -13,6 +13,7 @@
 #include <string.h>
 #include "anni_gpu_compat.h"
 #include "anni_lm_adam.h"
+#include "optstep_internal.h"
 
 static int g_offload_all;
 
@@ -150,8 +151,33 @@ extern "C" anni_lm_adam *anni_lm_adam_create(const anni_lm_tensor *tensors, int 
 	return opt;
 }
 
+/*
+** Nobody may keep a pointer into a flat that is about to go: matrix views set by
+** anni_lm_adam_alias are detached (unalias_segs, lang/lm_adam.c:146-165 of the reference), and
+** the gradient vectors registered by anni_lm_adam_alias_vec are forgotten.
+*/
+static void detach_views(anni_lm_adam *opt)
+{
+	for (int i = 0; i < opt->n_segs; i++) {
+		anni_lm_adam_seg *s = &opt->segs[i];
+
+		if (s->w_mat && opt->d_param && s->w_mat->d_data == opt->d_param + s->off) {
+			s->w_mat->d_data = NULL;
+			s->w_mat->on_device = 0;
+		}
+		if (s->dw_mat && opt->d_grad && s->dw_mat->d_data == (float *)opt->d_grad + s->off) {
+			s->dw_mat->d_data = NULL;
+			s->dw_mat->on_device = 0;
+		}
+		s->w_mat = s->dw_mat = NULL;
+	}
+	if (opt->d_grad)
+		anni_colsum_forget(opt->d_grad, (char *)opt->d_grad + (size_t)opt->n * 4u);
+}
+
 static void release_device(anni_lm_adam *opt)
 {
+	detach_views(opt);
 	if (opt->engine)
 		anni_optstep_destroy(opt->engine);
 	opt->engine = NULL;
@@ -181,18 +207,6 @@ extern "C" void anni_lm_adam_free(anni_lm_adam **popt)
 	opt = *popt;
 	if (opt->d_param)
 		(void)anni_lm_adam_sync_host(opt);	/* weights back to the host before the flats go (lm_adam.c:146-165) */
-	for (int i = 0; i < opt->n_segs; i++) {	/* detach the views: nobody may free a slice of a flat */
-		anni_lm_adam_seg *s = &opt->segs[i];
-
-		if (s->w_mat && s->w_mat->d_data == opt->d_param + s->off) {
-			s->w_mat->d_data = NULL;
-			s->w_mat->on_device = 0;
-		}
-		if (s->dw_mat && opt->d_grad && s->dw_mat->d_data == (float *)opt->d_grad + s->off) {
-			s->dw_mat->d_data = NULL;
-			s->dw_mat->on_device = 0;
-		}
-	}
 	if (opt->snap_stream) {
 		cudaStreamSynchronize((cudaStream_t)opt->snap_stream);
 		cudaEventDestroy((cudaEvent_t)opt->snap_event);
@@ -395,6 +409,30 @@ extern "C" int anni_lm_adam_alias(anni_lm_adam *opt, int tensor, anni_mat *w, an
 	return ANNI_OK;
 }
 
+extern "C" int anni_lm_adam_alias_vec(anni_lm_adam *opt, int tensor, float **d_w, void **d_dw)
+{
+	anni_lm_adam_seg *s;
+	void *grad_slice;
+
+	if (!opt || tensor < 0 || tensor >= opt->n_segs || !opt->d_param || !opt->d_grad)
+		return ANNI_E_ARG;
+	s = &opt->segs[tensor];
+	grad_slice = (char *)opt->d_grad + (size_t)s->off * elem_size(opt->grad_dtype);
+	if (s->dw) {
+		/* what the host vector holds so far goes over once; from now on the slice is the gradient */
+		if (upload_as(grad_slice, opt->grad_dtype, s->dw, s->n) != 0)
+			return ANNI_E_CUDA;
+		if (opt->grad_dtype == ANNI_DT_F32 && s->n <= 0x7fffffff)
+			(void)anni_colsum_register(s->dw, (float *)grad_slice, (int)s->n);
+		s->dw = NULL;
+	}
+	if (d_w)
+		*d_w = opt->d_param + s->off;
+	if (d_dw)
+		*d_dw = grad_slice;
+	return ANNI_OK;
+}
+
 extern "C" int anni_lm_adam_snapshot_begin(anni_lm_adam *opt)
 {
 	const size_t nb = opt ? (size_t)opt->n * elem_size(opt->state_dtype) : 0;
@@ -515,6 +553,21 @@ extern "C" int anni_lm_adam_sync_host(anni_lm_adam *opt)
 
 /* ---- the step ----------------------------------------------------------------------- */
 
+/* ANN_GNORM_EVERY=k: report the gradient norm every k-th step (adam_gnorm_every, lm_adam.c:438-450) */
+static int gnorm_every(void)
+{
+	static int every = -1;
+
+	if (every < 0) {
+		const char *e = getenv("ANN_GNORM_EVERY");
+
+		every = e ? atoi(e) : 0;
+		if (every < 0)
+			every = 0;
+	}
+	return every;
+}
+
 extern "C" int anni_lm_adam_step(anni_lm_adam *opt, double lr)
 {
 	return anni_lm_adam_step_scaled(opt, lr, 1.0);
@@ -555,8 +608,8 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	hp.flags = ANNI_STEP_ZERO_GRAD;
 	if (opt->exact_update)
 		hp.flags |= ANNI_STEP_EXACT_UPDATE;
-	/* the reference computes the norm (and may skip) only when it clips (lm_adam.c:466) */
-	if (opt->grad_clip > 0.0 || opt->loss_scale > 0.0)
+	/* the reference computes the norm (and may skip) only when it clips or reports it (lm_adam.c:466) */
+	if (opt->grad_clip > 0.0 || opt->loss_scale > 0.0 || gnorm_every() > 0)
 		hp.flags |= ANNI_STEP_CHECK_FINITE;
 	rc = anni_optstep_step(opt->engine, &hp, NULL);
 	if (rc != ANNI_OK)
@@ -571,8 +624,12 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	opt->last_skipped = st.skipped;
 	if (st.skipped)
 		fprintf(stderr, "[adam] step %d skipped: grad norm %g\n", opt->t, st.norm);
-	else
+	else {
 		opt->dev_mv = 1;
+		if (gnorm_every() > 0 && opt->t % gnorm_every() == 0)	/* lm_adam.c:484-487 */
+			fprintf(stderr, "[adam] step %d grad norm %.4g%s\n", opt->t, st.norm,
+			    opt->grad_clip > 0.0 && st.norm > opt->grad_clip ? " (clipped)" : "");
+	}
 	if (host_grads)			/* seg_scatter zeroes the host gradient vectors (lm_adam.c:413) */
 		for (i = 0; i < opt->n_segs; i++)
 			if (opt->segs[i].dw)

@@ -26,7 +26,10 @@
 **     (and sizes the launch).  Make that first call during start-up, before any
 **     stream capture is begun on that device;
 **   - the dynamic loss-scale state machine lives in an engine's own block and is
-**     not available here: pass the loss scale folded into grad_scale.
+**     not available here: pass the loss scale folded into grad_scale;
+**   - cfg->seg_off and cfg->seg_flags are read from host memory during the call
+**     (they must stay valid until it returns, not longer), and a stream that is
+**     being captured is refused with ANNI_E_ARG.
 ** No cudaMalloc, cudaFree, or other allocating routine is called on any path
 ** below; the caller supplies every input and output buffer.
 */
@@ -45,6 +48,7 @@ struct noalloc_scratch {
 	uint32_t	seg_flags[ANNI_NOALLOC_MAX_SEG];
 	float		seg_amax[ANNI_NOALLOC_MAX_SEG];
 	float		seg_scale[ANNI_NOALLOC_MAX_SEG];
+	uint32_t	seg_done[ANNI_NOALLOC_MAX_SEG];	/* per-tensor arrival counters (fp8 twins) */
 };
 
 /*
@@ -76,6 +80,7 @@ __global__ void noalloc_clear_kernel(int n_seg)
 	if (i < n_seg) {
 		s->seg_amax[i] = 0.0f;
 		s->seg_scale[i] = 0.0f;
+		s->seg_done[i] = 0u;
 	}
 }
 
@@ -84,6 +89,7 @@ namespace {
 struct per_device {
 	noalloc_scratch	*ptr;		/* device address of g_noalloc_scratch on this device */
 	int		blocks[2][2];	/* persistent grid per (grad dtype, state dtype) */
+	int		sc_log2;	/* super-chunk size, as the engines use it */
 	bool		ready;
 };
 
@@ -106,8 +112,8 @@ int device_setup(int dev, per_device **out)
 			return ANNI_E_CUDA;
 		for (int g = 0; g < 2; g++)
 			for (int s = 0; s < 2; s++) {
-				d->blocks[g][s] = anni_grid_blocks(g, s, 1);
-				if (d->blocks[g][s] < 1)
+				/* the engines' own geometry: same grid, same block partials, same norm bits */
+				if (anni_engine_geometry(g, s, &d->blocks[g][s], &d->sc_log2) != ANNI_OK)
 					return ANNI_E_CUDA;
 			}
 		d->ptr = static_cast<noalloc_scratch *>(p);
@@ -174,6 +180,16 @@ extern "C" int anni_optstep_step_noalloc(const anni_optstep_config *cfg,
 		return ANNI_E_ARG;
 	if (cudaGetDevice(&dev) != cudaSuccess)
 		return ANNI_E_CUDA;
+	{
+		/* the tensor table travels from the caller's host memory with every call: a captured
+		** copy would replay from an address that may be gone, so a capturing stream is refused */
+		cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+
+		if (cudaStreamIsCapturing(st, &cap) != cudaSuccess)
+			return ANNI_E_CUDA;
+		if (cap != cudaStreamCaptureStatusNone)
+			return ANNI_E_ARG;
+	}
 	rc = device_setup(dev, &d);
 	if (rc != ANNI_OK)
 		return rc;
@@ -194,10 +210,12 @@ extern "C" int anni_optstep_step_noalloc(const anni_optstep_config *cfg,
 	la.seg_flags = d->ptr->seg_flags;
 	la.seg_amax = d->ptr->seg_amax;
 	la.seg_scale = d->ptr->seg_scale;
+	la.seg_done = d->ptr->seg_done;
 	la.n_seg = n_seg;
-	la.sc_log2 = 2;
+	la.sc_log2 = d->sc_log2;
+	la.pipe_lag = ANNI_PIPE_LAG;
 	la.ctl = &d->ptr->ctl;
-	la.flags = has_fp8 ? ANNI_LAUNCH_HAS_FP8 : 0;
+	la.flags = has_fp8 ? (ANNI_LAUNCH_HAS_FP8 | ANNI_LAUNCH_FP8_PIPE) : 0;
 	rc = anni_fill_hyper(&la, hp);
 	if (rc != ANNI_OK)
 		return rc;

@@ -114,6 +114,49 @@ __device__ __forceinline__ float rcp_approx_ftz(float x)
 	return r;
 }
 
+/*
+** (double)x built with integer instructions instead of the conversion unit.  B200 converts
+** 16 values per clock and SM (the same unit runs the square roots and reciprocals), which
+** makes conversions, not memory, the limit of the norm pass and of the double-precision
+** update; shifts and adds run four to eight times as wide.  A normal float widens by
+** re-biasing the exponent (+896) and moving the mantissa up 29 bits; zero keeps its sign;
+** subnormals, infinities and NaNs (rare) take the hardware conversion.  Bit-identical to
+** (double)x for every input.
+*/
+__device__ __forceinline__ double widen_alu(float x)
+{
+	const uint32_t b = __float_as_uint(x);
+	const uint32_t a = b & 0x7fffffffu;
+	const bool normal = a - 0x00800000u < 0x7f000000u;
+
+	if (normal || a == 0u)
+		return __hiloint2double((int)((b & 0x80000000u) | ((a >> 3) + (normal ? 0x38000000u : 0u))),
+		    (int)(b << 29));
+	return (double)x;
+}
+
+/* (double)x by whichever route the build assigns to this use (bit k of `mask`) */
+template <int MASK, int BIT>
+__device__ __forceinline__ double widen(float x)
+{
+	return (MASK >> BIT) & 1 ? widen_alu(x) : (double)x;
+}
+
+/*
+** x rounded to 24 significant bits, still a double: Veltkamp's split with 2^29 + 1.  For x
+** inside the float range this is (double)(float)x -- computed in the double-precision pipe
+** instead of a narrowing and a widening conversion -- except that a value exactly half way
+** between two floats (one in 2^29) may round to either neighbour.  The exact update uses it
+** for the operands of the update term only; what is STORED is always rounded by the
+** conversion proper.
+*/
+__device__ __forceinline__ double round_to_24_bits(double x)
+{
+	const double c = __dmul_rn(x, 536870913.0);
+
+	return __dsub_rn(c, __dsub_rn(c, x));
+}
+
 __device__ __forceinline__ f32x8 unpack_bf16x8(uint4 q)
 {
 	f32x8 r;
@@ -264,6 +307,13 @@ template <> struct io4<float> {
 		__stcs(reinterpret_cast<uint4 *>(static_cast<float *>(base) + e),
 		    make_uint4(__float_as_uint(r.x[0]), __float_as_uint(r.x[1]), __float_as_uint(r.x[2]),
 		    __float_as_uint(r.x[3])));
+	}
+	/* same, default cache policy: for lines that are read again soon and should wait in L2 */
+	static __device__ __forceinline__ void store_keep(void *base, uint64_t e, const f32x4 &r)
+	{
+		*reinterpret_cast<uint4 *>(static_cast<float *>(base) + e) =
+		    make_uint4(__float_as_uint(r.x[0]), __float_as_uint(r.x[1]), __float_as_uint(r.x[2]),
+		    __float_as_uint(r.x[3]));
 	}
 	static __device__ __forceinline__ void zero(void *base, uint64_t e)
 	{
@@ -433,8 +483,9 @@ __device__ __forceinline__ void norm_accumulate(const f32x8 &g, double &acc0, do
 	** agree with a double accumulation to the last bits */
 #pragma unroll
 	for (int k = 0; k < ANNI_VEC; k += 2) {
-		const double g0 = (double)g.x[k];
-		const double g1 = (double)g.x[k + 1];
+		/* the widenings are shared out between the conversion unit and the integer pipe */
+		const double g0 = k < ANNI_NORM_ALU_LANES ? widen_alu(g.x[k]) : (double)g.x[k];
+		const double g1 = k + 1 < ANNI_NORM_ALU_LANES ? widen_alu(g.x[k + 1]) : (double)g.x[k + 1];
 
 		acc0 = fma(g0, g0, acc0);
 		acc1 = fma(g1, g1, acc1);
@@ -530,9 +581,10 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	float gf, float &p, float &m, float &v)
 {
 	/* moments: the reference's double expression, each product and the sum rounded on its own */
-	const double g = __dmul_rn((double)gf, coef);
-	const double md = __dadd_rn(__dmul_rn(a.b1, (double)m), __dmul_rn(a.omb1, g));
-	const double vd = __dadd_rn(__dmul_rn(a.b2, (double)v), __dmul_rn(__dmul_rn(a.omb2, g), g));
+	constexpr int W = EXACT ? ANNI_WIDEN_EXACT : ANNI_WIDEN_FAST;
+	const double g = __dmul_rn(widen<W, 0>(gf), coef);
+	const double md = __dadd_rn(__dmul_rn(a.b1, widen<W, 1>(m)), __dmul_rn(a.omb1, g));
+	const double vd = __dadd_rn(__dmul_rn(a.b2, widen<W, 2>(v)), __dmul_rn(__dmul_rn(a.omb2, g), g));
 
 	m = __double2float_rn(md);
 	v = __double2float_rn(vd);
@@ -551,7 +603,9 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 		** (relative error ~1e-12), so p - u rounds to the reference's float in
 		** all but about one element in ten million.
 		*/
-		const double vr = (double)v;
+		/* the rounded moments as doubles, without going through the conversion unit twice */
+		const double vr = ANNI_EXACT_SPLIT ? round_to_24_bits(vd) : (double)v;
+		const double mr = ANNI_EXACT_SPLIT ? round_to_24_bits(md) : (double)m;
 		const double x = vr * a.ibc2d;
 		const double hx = vr * (0.5 * a.ibc2d);
 		double y;
@@ -563,10 +617,15 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 
 		asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(q) : "d"(dn));
 		q = fma(fma(-dn, q, 1.0), q, q);
-		const float p1 = __double2float_rn((double)p - (a.lrbc1d * (double)m) * q);
+		const double pd = widen<W, 3>(p) - (a.lrbc1d * mr) * q;
 
 		/* decay on the stored float, in double as the reference does, rounded once */
-		p = lrwd != 0.0f ? __double2float_rn(fma(-a.lrwdd, (double)p1, (double)p1)) : p1;
+		if (lrwd != 0.0f) {
+			const double p1 = ANNI_EXACT_SPLIT ? round_to_24_bits(pd) : (double)__double2float_rn(pd);
+
+			p = __double2float_rn(fma(-a.lrwdd, p1, p1));
+		} else
+			p = __double2float_rn(pd);
 		return;
 	}
 	/*
@@ -583,7 +642,28 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	p = __fmaf_rn(-lrwd, p, p);
 }
 
-template <typename GradT, typename StateT, bool EXACT>
+/* "the step leaves the gradients zeroed": the bound buffer, or every part of the rank's full arena */
+template <typename GradT>
+__device__ __forceinline__ void zero_grad4(const anni_launch &a, uint64_t e)
+{
+	if (a.zero_parts > 0) {
+		for (int k = 0; k < a.zero_parts; k++)
+			io4<GradT>::zero(a.zero_base, (uint64_t)k * a.zero_stride + e);
+	} else
+		io4<GradT>::zero(a.grad, e);
+}
+
+template <typename GradT>
+__device__ __forceinline__ void zero_grad1(const anni_launch &a, uint64_t i)
+{
+	if (a.zero_parts > 0) {
+		for (int k = 0; k < a.zero_parts; k++)
+			io8<GradT>::store1(a.zero_base, (uint64_t)k * a.zero_stride + i, 0.0f);
+	} else
+		io8<GradT>::store1(a.grad, i, 0.0f);
+}
+
+template <typename GradT, typename StateT, bool EXACT, bool PIPE = false>
 __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t e, double coef,
 	uint32_t sflags, float &tmax, uint64_t seg_base, int64_t pack_off, uint32_t pack_ld,
 	uint32_t pack_cols)
@@ -597,7 +677,10 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 #pragma unroll
 	for (int k = 0; k < ANNI_UVEC; k++)
 		adam_elem<EXACT>(a, coef, lrwd, g.x[k], p.x[k], m.x[k], v.x[k]);
-	io4<float>::store(a.master, e, p);
+	if (PIPE && (sflags & ANNI_SEG_TWIN_FP8) && !(a.flags & ANNI_LAUNCH_PIPE_STREAM))
+		io4<float>::store_keep(a.master, e, p);	/* read back for its e4m3 code while still in L2 */
+	else
+		io4<float>::store(a.master, e, p);
 	io4<StateT>::store(a.m, e, m);
 	io4<StateT>::store(a.v, e, v);
 	if ((sflags & ANNI_SEG_TWIN_BF16) && a.twin16) {
@@ -626,7 +709,7 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 		    + (ws - r * pack_cols), p);
 	}
 	if (a.flags & ANNI_STEP_ZERO_GRAD)
-		io4<GradT>::zero(a.grad, e);
+		zero_grad4<GradT>(a, e);
 }
 
 /* element-wise path for chunks that cross a tensor boundary, the arena end, or unaligned buffers */
@@ -671,7 +754,7 @@ __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64
 			}
 		}
 		if (a.flags & ANNI_STEP_ZERO_GRAD)
-			io8<GradT>::store1(a.grad, i, 0.0f);
+			zero_grad1<GradT>(a, i);
 	}
 }
 
@@ -688,7 +771,7 @@ __device__ __forceinline__ void amax_flush(const anni_launch &a, int seg, float 
 }
 
 /* one chunk the general way: tensor looked up from scratch, element-wise when the chunk is not whole */
-template <typename GradT, typename StateT, bool EXACT>
+template <typename GradT, typename StateT, bool EXACT, bool PIPE>
 __device__ __forceinline__ void update_chunk_general(const anni_launch &a, const decision &d, uint64_t base,
 	uint64_t t4, float &tmax, int &amax_seg)
 {
@@ -708,83 +791,16 @@ __device__ __forceinline__ void update_chunk_general(const anni_launch &a, const
 		if (a.seg_aux) {
 			const anni_seg_derived ax = a.seg_aux[seg];
 
-			update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax,
+			update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base + t4, d.coef, sflags, tmax,
 			    (uint64_t)a.seg_off[seg] - a.arena_off, ax.pack_off, (uint32_t)ax.pack_ld,
 			    (uint32_t)ax.cols);
 		} else
-			update_chunk_vec<GradT, StateT, EXACT>(a, base + t4, d.coef, sflags, tmax, 0, 0, 0, 1);
+			update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base + t4, d.coef, sflags, tmax, 0, 0, 0, 1);
 	} else if (whole) {
-		io4<GradT>::zero(a.grad, base + t4);	/* skipped step: only the gradients change */
+		zero_grad4<GradT>(a, base + t4);	/* skipped step: only the gradients change */
 	} else
 		update_chunk_scalar<GradT, StateT, EXACT>(a, base + t4, d.coef, d.skip);
 }
-
-/*
-** The blocks walk their super-chunks (2^sc_log2 consecutive chunks) from the last to the
-** first.  A super-chunk that lies wholly inside the shard and inside one tensor -- all but a
-** few hundred of them -- takes the short road: tensor flags looked up once, then nothing
-** but loads, arithmetic and stores per chunk.  The others go chunk by chunk the general way.
-*/
-template <typename GradT, typename StateT, bool EXACT>
-__device__ __forceinline__ void update_phase(const anni_launch &a, const decision &d)
-{
-	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_UCHUNK_LOG2);
-	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
-	const uint32_t per = 1u << w.sc;			/* chunks per super-chunk */
-	const uint64_t span = (uint64_t)ANNI_UCHUNK << w.sc;	/* elements per super-chunk */
-	float tmax = 0.0f;
-	int seg = -1;
-	int amax_seg = -1;
-
-	if (d.skip && !(a.flags & ANNI_STEP_ZERO_GRAD))
-		return;
-	/* backwards: the chunks read last by the norm phase are the likeliest to sit in L2 */
-	for (uint64_t r = w.iters >> w.sc; r > 0; r--) {
-		const uint64_t c0 = ((r - 1) * gridDim.x + blockIdx.x) << w.sc;
-		const uint64_t base0 = c0 * ANNI_UCHUNK;
-		const int64_t alo = (int64_t)(a.arena_off + base0);
-
-		if (c0 >= w.chunks)
-			continue;
-		if (seg < 0)
-			seg = seg_find(a.seg_off, a.n_seg, alo);
-		while (alo < a.seg_off[seg])
-			seg--;
-		if (!d.skip && a.aligned && base0 + span <= a.n && alo + (int64_t)span <= a.seg_off[seg + 1]) {
-			const uint32_t sflags = a.seg_flags[seg];
-
-			if (amax_seg != seg) {
-				if (amax_seg >= 0)
-					amax_flush(a, amax_seg, tmax);
-				amax_seg = (sflags & ANNI_SEG_TWIN_FP8) ? seg : -1;
-			}
-			if (a.seg_aux) {
-				const anni_seg_derived ax = a.seg_aux[seg];
-				const uint64_t seg_base = (uint64_t)a.seg_off[seg] - a.arena_off;
-
-#pragma unroll 1
-				for (uint32_t k = per; k > 0; k--)
-					update_chunk_vec<GradT, StateT, EXACT>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
-					    d.coef, sflags, tmax, seg_base, ax.pack_off, (uint32_t)ax.pack_ld,
-					    (uint32_t)ax.cols);
-			} else {
-#pragma unroll 1
-				for (uint32_t k = per; k > 0; k--)
-					update_chunk_vec<GradT, StateT, EXACT>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
-					    d.coef, sflags, tmax, 0, 0, 0, 1);
-			}
-		} else {
-			for (uint32_t k = per; k > 0; k--)
-				if (c0 + (k - 1) < w.chunks)
-					update_chunk_general<GradT, StateT, EXACT>(a, d, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK,
-					    t4, tmax, amax_seg);
-		}
-	}
-	if (amax_seg >= 0)
-		amax_flush(a, amax_seg, tmax);
-}
-
-/* ---- phase C: e4m3 twins of the fresh master ------------------------------- */
 
 /* dequantisation scale of a tensor from its amax (num/gpu_cuda.cu:927-938 of the reference) */
 __device__ __forceinline__ float fp8_scale(float amax)
@@ -815,6 +831,206 @@ __device__ __forceinline__ void store_e4m3x4(const anni_launch &a, uint64_t e, u
 	} else
 		__stcs(reinterpret_cast<uint32_t *>(a.twin8 + e), q);
 }
+
+/*
+** One-launch step with e4m3 twins: the quantiser runs BEHIND the update, tensor by tensor,
+** instead of as a second pass over the whole arena after a grid barrier.  A tensor's codes
+** need its amax, i.e. every block must have finished updating it; re-reading its fresh
+** master from HBM afterwards costs 4 bytes per element.  So each block reports a tensor as
+** soon as its own (descending) walk has left it behind -- after flushing its amax share --
+** and, a little later, quantises its share of that tensor: by then the whole grid has
+** reported it (the blocks move in step), the per-tensor wait ends at once, and the master
+** lines written minutes of nanoseconds ago are still in the 126 MB L2 (they are stored with
+** the default policy; everything else streams through with evict-first hints).  The wait is
+** bounded like the grid barrier and gives up at once when any block has raised an error.
+*/
+__device__ __forceinline__ bool pipe_wants(const anni_launch &a, int s)
+{
+	return (a.seg_flags[s] & ANNI_SEG_TWIN_FP8) && !(a.seg_aux && a.seg_aux[s].fp8_t_off >= 0);
+}
+
+/* this block will not touch tensor s again (block-uniform call) */
+__device__ __forceinline__ void pipe_report(const anni_launch &a, int s)
+{
+	if (!pipe_wants(a, s))
+		return;
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		__threadfence();
+		atomicAdd(&a.seg_done[s], 1u);
+	}
+}
+
+/* this block's share of tensor s's e4m3 codes; false when the wait for the other blocks gave up */
+__device__ __forceinline__ bool pipe_quantize(const anni_launch &a, int s)
+{
+	__shared__ int s_ok;
+
+	if (!pipe_wants(a, s))
+		return true;
+	const int64_t t_lo = max(a.seg_off[s], (int64_t)a.arena_off) - (int64_t)a.arena_off;
+	const int64_t t_hi = min(a.seg_off[s + 1], (int64_t)(a.arena_off + a.n)) - (int64_t)a.arena_off;
+
+	if (t_lo >= t_hi)
+		return true;		/* not in this shard */
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		uint32_t polls = 0;
+		int ok = 1;
+
+		while (ld_acquire_u32(&a.seg_done[s]) < gridDim.x) {
+			__nanosleep(32);
+			if (++polls > ANNI_WAIT_POLLS || ld_acquire_u32(reinterpret_cast<const uint32_t *>(&a.ctl->error)) != 0) {
+				ok = 0;
+				atomicCAS(&a.ctl->error, 0, ANNI_E_BARRIER_TIMEOUT);
+				break;
+			}
+		}
+		if (polls)
+			atomicAdd(&a.ctl->pipe_polls, polls);
+		__threadfence();
+		s_ok = ok;
+	}
+	__syncthreads();
+	if (!s_ok)
+		return false;
+	const float scale = fp8_scale(__ldcg(&a.seg_amax[s]));
+	const float inv = __fdiv_rn(1.0f, scale);
+	const uint64_t lo = (uint64_t)t_lo;
+	const uint64_t hi = (uint64_t)t_hi;
+	const uint64_t c_hi = (hi + ANNI_UCHUNK - 1) >> ANNI_UCHUNK_LOG2;
+	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
+	const uint64_t G = gridDim.x;
+
+	if (blockIdx.x == 0 && threadIdx.x == 0)
+		a.seg_scale[s] = scale;
+	for (uint64_t c = (lo >> ANNI_UCHUNK_LOG2) + blockIdx.x; c < c_hi; c += 4 * G) {
+		/* four chunks per trip, their loads issued together */
+		if (a.aligned && (c << ANNI_UCHUNK_LOG2) >= lo && ((c + 3 * G + 1) << ANNI_UCHUNK_LOG2) <= hi) {
+			const uint64_t e0 = (c << ANNI_UCHUNK_LOG2) + t4;
+			const uint64_t st = G << ANNI_UCHUNK_LOG2;
+			const f32x4 p0 = io4<float>::load(a.master, e0);
+			const f32x4 p1 = io4<float>::load(a.master, e0 + st);
+			const f32x4 p2 = io4<float>::load(a.master, e0 + 2 * st);
+			const f32x4 p3 = io4<float>::load(a.master, e0 + 3 * st);
+
+			store_e4m3x4(a, e0, e4m3x4(p0, inv));
+			store_e4m3x4(a, e0 + st, e4m3x4(p1, inv));
+			store_e4m3x4(a, e0 + 2 * st, e4m3x4(p2, inv));
+			store_e4m3x4(a, e0 + 3 * st, e4m3x4(p3, inv));
+			continue;
+		}
+		for (int k = 0; k < 4; k++) {
+			const uint64_t ck = c + (uint64_t)k * G;
+			const uint64_t e = (ck << ANNI_UCHUNK_LOG2) + t4;
+
+			if (ck >= c_hi)
+				break;
+			if (a.aligned && (ck << ANNI_UCHUNK_LOG2) >= lo && ((ck + 1) << ANNI_UCHUNK_LOG2) <= hi) {
+				store_e4m3x4(a, e, e4m3x4(io4<float>::load(a.master, e), inv));
+				continue;
+			}
+			for (int j = 0; j < ANNI_UVEC; j++)	/* the tensor's ragged ends, its own elements only */
+				if (e + j >= lo && e + j < hi)
+					a.twin8[e + j] = (uint8_t)__nv_cvt_float_to_fp8(a.master[e + j] * inv,
+					    __NV_SATFINITE, __NV_E4M3);
+		}
+	}
+	return true;
+}
+
+/*
+** The blocks walk their super-chunks (2^sc_log2 consecutive chunks) from the last to the
+** first.  A super-chunk that lies wholly inside the shard and inside one tensor -- all but a
+** few hundred of them -- takes the short road: tensor flags looked up once, then nothing
+** but loads, arithmetic and stores per chunk.  The others go chunk by chunk the general way.
+*/
+template <typename GradT, typename StateT, bool EXACT, bool PIPE>
+__device__ __forceinline__ bool update_phase(const anni_launch &a, const decision &d)
+{
+	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_UCHUNK_LOG2);
+	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
+	const uint32_t per = 1u << w.sc;			/* chunks per super-chunk */
+	const uint64_t span = (uint64_t)ANNI_UCHUNK << w.sc;	/* elements per super-chunk */
+	const int64_t lag = (int64_t)(gridDim.x * span) * (a.pipe_lag > 0 ? a.pipe_lag : 1);	/* PIPE: rounds of the whole grid */
+	float tmax = 0.0f;
+	int seg = -1;
+	int amax_seg = -1;
+	int rep_hi = a.n_seg - 1;	/* PIPE: highest tensor this block has not reported yet */
+	int q_hi = a.n_seg - 1;		/* PIPE: highest tensor this block has not quantised its share of */
+
+	if (d.skip && !(a.flags & ANNI_STEP_ZERO_GRAD))
+		return true;
+	/* backwards: the chunks read last by the norm phase are the likeliest to sit in L2 */
+	for (uint64_t r = w.iters >> w.sc; r > 0; r--) {
+		const uint64_t c0 = ((r - 1) * gridDim.x + blockIdx.x) << w.sc;
+		const uint64_t base0 = c0 * ANNI_UCHUNK;
+		const int64_t alo = (int64_t)(a.arena_off + base0);
+
+		if (c0 >= w.chunks)
+			continue;
+		if (PIPE && !d.skip) {
+			const int64_t top = alo + (int64_t)span;	/* this and all later super-chunks lie below */
+
+			while (rep_hi >= 0 && a.seg_off[rep_hi] >= top) {
+				if (amax_seg >= rep_hi) {
+					amax_flush(a, amax_seg, tmax);
+					amax_seg = -1;
+				}
+				pipe_report(a, rep_hi--);
+			}
+			while (q_hi > rep_hi && a.seg_off[q_hi] >= top + lag)
+				if (!pipe_quantize(a, q_hi--))
+					return false;
+		}
+		if (seg < 0)
+			seg = seg_find(a.seg_off, a.n_seg, alo);
+		while (alo < a.seg_off[seg])
+			seg--;
+		if (!d.skip && a.aligned && base0 + span <= a.n && alo + (int64_t)span <= a.seg_off[seg + 1]) {
+			const uint32_t sflags = a.seg_flags[seg];
+
+			if (amax_seg != seg) {
+				if (amax_seg >= 0)
+					amax_flush(a, amax_seg, tmax);
+				amax_seg = (sflags & ANNI_SEG_TWIN_FP8) ? seg : -1;
+			}
+			if (a.seg_aux) {
+				const anni_seg_derived ax = a.seg_aux[seg];
+				const uint64_t seg_base = (uint64_t)a.seg_off[seg] - a.arena_off;
+
+#pragma unroll 1
+				for (uint32_t k = per; k > 0; k--)
+					update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
+					    d.coef, sflags, tmax, seg_base, ax.pack_off, (uint32_t)ax.pack_ld,
+					    (uint32_t)ax.cols);
+			} else {
+#pragma unroll 1
+				for (uint32_t k = per; k > 0; k--)
+					update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
+					    d.coef, sflags, tmax, 0, 0, 0, 1);
+			}
+		} else {
+			for (uint32_t k = per; k > 0; k--)
+				if (c0 + (k - 1) < w.chunks)
+					update_chunk_general<GradT, StateT, EXACT, PIPE>(a, d, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK,
+					    t4, tmax, amax_seg);
+		}
+	}
+	if (amax_seg >= 0)
+		amax_flush(a, amax_seg, tmax);
+	if (PIPE && !d.skip) {
+		/* the walk is over: report what is left, then quantise what is left */
+		while (rep_hi >= 0)
+			pipe_report(a, rep_hi--);
+		while (q_hi >= 0)
+			if (!pipe_quantize(a, q_hi--))
+				return false;
+	}
+	return true;
+}
+
+/* ---- phase C: e4m3 twins of the fresh master ------------------------------- */
 
 /* one chunk the general way: element-wise when it is not whole */
 __device__ __forceinline__ void quantize_chunk_general(const anni_launch &a, uint64_t base, uint64_t t4)
@@ -1183,13 +1399,18 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_laun
 			a.ctl->skipped = d.skip ? 1 : 0;
 		}
 	}
-	update_phase<GradT, StateT, EXACT>(a, d);
+	update_phase<GradT, StateT, EXACT, false>(a, d);
 	if (!(a.flags & ANNI_LAUNCH_NO_EPILOGUE))
 		step_epilogue(a.ctl, d.skip);
 }
 
-/* The whole step in one cooperative launch. */
-template <typename GradT, typename StateT, bool EXACT>
+/*
+** The whole step in one cooperative launch.  PIPE (chosen when some tensor wants an e4m3
+** twin): the quantiser follows the update tensor by tensor inside the update phase; block 0
+** clears the per-tensor amax and arrival counters before the first barrier, so the step needs
+** no memset ahead of it.
+*/
+template <typename GradT, typename StateT, bool EXACT, bool PIPE>
 __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launch a)
 {
 	decision d;
@@ -1197,14 +1418,22 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launc
 	uint32_t barriers = 0;
 	const double loss_scale = a.ctl->loss_scale;
 
-	if (a.flags & ANNI_LAUNCH_NEED_NORM) {
-		double s = block_sum(norm_phase<GradT>(a));
+	if (PIPE && blockIdx.x == 0)
+		for (int s = threadIdx.x; s < a.n_seg; s += blockDim.x) {
+			a.seg_amax[s] = 0.0f;
+			a.seg_done[s] = 0u;
+		}
+	if ((a.flags & ANNI_LAUNCH_NEED_NORM) || PIPE) {
+		double s = 0.0;
 
+		if (a.flags & ANNI_LAUNCH_NEED_NORM)
+			s = block_sum(norm_phase<GradT>(a));
 		if (threadIdx.x == 0)
 			a.ctl->partials[blockIdx.x] = s;
 		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
 			return;
-		ss = sum_partials(a.ctl, (int)gridDim.x);
+		if (a.flags & ANNI_LAUNCH_NEED_NORM)
+			ss = sum_partials(a.ctl, (int)gridDim.x);
 	}
 	d = decide(a, ss, 0.0, loss_scale);
 	if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -1214,8 +1443,9 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launc
 		a.ctl->eff_scale = d.coef;
 		a.ctl->skipped = d.skip ? 1 : 0;
 	}
-	update_phase<GradT, StateT, EXACT>(a, d);
-	if ((a.flags & ANNI_LAUNCH_HAS_FP8) && !d.skip) {
+	if (!update_phase<GradT, StateT, EXACT, PIPE>(a, d))
+		return;
+	if (!PIPE && (a.flags & ANNI_LAUNCH_HAS_FP8) && !d.skip) {
 		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
 			return;
 		quantize_phase(a);
@@ -1353,6 +1583,23 @@ __global__ void __launch_bounds__(ANNI_THREADS) quantize_transposed_kernel(const
 	}
 }
 
+/*
+** ZeRO-1: what the update's own walk cannot reach of a rank's full gradient arena -- elements
+** [from, stride) of every part, when this rank's shard is shorter than the others' (the last
+** rank, or a rank without elements).  Usually a few thousand elements.
+*/
+template <typename T>
+__global__ void __launch_bounds__(ANNI_THREADS) zero_tail_kernel(T *arena, uint64_t from, uint64_t stride,
+	int parts)
+{
+	const uint64_t len = stride - from;
+	const uint64_t total = len * (uint64_t)parts;
+
+	for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+	    i += (uint64_t)gridDim.x * blockDim.x)
+		arena[(i / len) * stride + from + i % len] = 0;
+}
+
 /* One-shot fp32 -> bf16 of a flat buffer (seeding the twin; num/gpu.h:73 of the reference). */
 __global__ void __launch_bounds__(ANNI_THREADS) f32_to_bf16_kernel(uint16_t *dst, const float *src,
 	uint64_t n, int aligned)
@@ -1423,23 +1670,33 @@ template <typename GradT, typename StateT>
 int launch_fused_t(const anni_launch *a, int blocks, cudaStream_t st)
 {
 	void *args[] = { (void *)a };
+	const bool pipe = (a->flags & ANNI_LAUNCH_FP8_PIPE) && (a->flags & ANNI_LAUNCH_HAS_FP8);
 	const void *k = (a->flags & ANNI_STEP_EXACT_UPDATE)
-	    ? (const void *)fused_kernel<GradT, StateT, true>
-	    : (const void *)fused_kernel<GradT, StateT, false>;
+	    ? (pipe ? (const void *)fused_kernel<GradT, StateT, true, true>
+	    : (const void *)fused_kernel<GradT, StateT, true, false>)
+	    : (pipe ? (const void *)fused_kernel<GradT, StateT, false, true>
+	    : (const void *)fused_kernel<GradT, StateT, false, false>);
 
 	return cudaLaunchCooperativeKernel(k, dim3(blocks), dim3(ANNI_THREADS), args, 0, st)
 	    == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
 
-/* resident blocks of the heavier (exact) variant: both variants then run with the same grid */
+/* resident blocks of the heaviest variant: every variant then runs with the same grid */
 template <typename GradT, typename StateT> int grid_t(int cooperative)
 {
-	const int a = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true>)
+	int best = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true, false>)
 	    : occupancy_blocks(update_kernel<GradT, StateT, true>);
-	const int b = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false>)
-	    : occupancy_blocks(update_kernel<GradT, StateT, false>);
+	const int others[3] = {
+		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false, false>)
+		    : occupancy_blocks(update_kernel<GradT, StateT, false>),
+		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true, true>) : best,
+		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false, true>) : best,
+	};
 
-	return a < b ? a : b;
+	for (int k = 0; k < 3; k++)
+		if (others[k] < best)
+			best = others[k];
+	return best;
 }
 
 /*
@@ -1558,6 +1815,26 @@ extern "C" int anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int
 		reduce_norm_kernel<__nv_bfloat16><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	else
 		reduce_norm_kernel<float><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	anni_count_launch();
+	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
+}
+
+extern "C" int anni_launch_zero_tail(void *arena, int grad_dtype, uint64_t from, uint64_t stride, int parts,
+	cudaStream_t st)
+{
+	uint64_t total;
+	int blocks;
+
+	if (!arena || from > stride || parts < 1)
+		return ANNI_E_ARG;
+	total = (stride - from) * (uint64_t)parts;
+	if (total == 0)
+		return ANNI_OK;
+	blocks = (int)((total + ANNI_THREADS - 1) / ANNI_THREADS < 4096 ? (total + ANNI_THREADS - 1) / ANNI_THREADS : 4096);
+	if (grad_dtype == ANNI_DT_BF16)
+		zero_tail_kernel<uint16_t><<<blocks, ANNI_THREADS, 0, st>>>((uint16_t *)arena, from, stride, parts);
+	else
+		zero_tail_kernel<uint32_t><<<blocks, ANNI_THREADS, 0, st>>>((uint32_t *)arena, from, stride, parts);
 	anni_count_launch();
 	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }

@@ -18,6 +18,7 @@ struct anni_optstep {
 	uint32_t		*d_seg_flags;
 	float			*d_amax;
 	float			*d_scale;
+	uint32_t		*d_seg_done;	/* per-tensor arrival counters of the one-launch fp8 step */
 	anni_seg_derived	*d_aux;		/* derived-twin table (anni_optstep_set_derived) */
 	int64_t			*d_tile_prefix;	/* tiles before each tensor, transposed e4m3 twins */
 	int64_t			n_tiles;
@@ -30,9 +31,34 @@ struct anni_optstep {
 	int			blocks_coop;
 	int			blocks_split;
 	int			blocks_rn;	/* grid of the fused reduce-scatter + norm kernel */
+	int			fp8_pipe;	/* one-launch fp8 step: quantise behind the update (default) */
+	int			fp8_stream;
+	/* ZeRO-1: this rank's full gradient arena, cleared by the update instead of the bound shard */
+	void			*grad_arena;
+	uint64_t		grad_arena_stride;
+	int			grad_arena_parts;
 };
 
 static int derived_after_step(anni_optstep *h, const anni_launch *la, cudaStream_t st);
+
+/* split form: the update clears the rank's full gradient arena, if one was named */
+static void use_grad_arena(const anni_optstep *h, anni_launch *la)
+{
+	if (h->grad_arena && (la->flags & ANNI_STEP_ZERO_GRAD)) {
+		la->zero_base = h->grad_arena;
+		la->zero_stride = h->grad_arena_stride;
+		la->zero_parts = h->grad_arena_parts;
+	}
+}
+
+/* ... and what lies beyond this shard's length in every part, which the update's walk never visits */
+static int zero_arena_tail(const anni_optstep *h, const anni_launch *la, cudaStream_t st)
+{
+	if (la->zero_parts < 1 || h->cfg.shard_n >= h->grad_arena_stride)
+		return ANNI_OK;
+	return anni_launch_zero_tail(h->grad_arena, h->cfg.grad_dtype, h->cfg.shard_n, h->grad_arena_stride,
+	    h->grad_arena_parts, st);
+}
 
 /* ANNI_B200_SUPERCHUNK=k: 2^k consecutive chunks per block per round (tuning knob). */
 static int superchunk_log2(void)
@@ -41,6 +67,36 @@ static int superchunk_log2(void)
 	int k = e ? atoi(e) : 2;
 
 	return k < 0 ? 0 : (k > 20 ? 20 : k);
+}
+
+/*
+** Launch geometry of the step kernels for the given dtypes on the current device: the
+** persistent grid (the same for the one-launch and the split form, so that their block
+** partials, and with them the norm's bits, agree) and the super-chunk size.  Every path that
+** launches those kernels -- engines and the allocation-free entry point -- asks here, so they
+** all honour the tuning knobs and report identical norms.
+*/
+extern "C" int anni_engine_geometry(int grad_dtype, int state_dtype, int *blocks, int *sc_log2)
+{
+	const char *e = getenv("ANNI_B200_BLOCKS_PER_SM");	/* fewer resident blocks than fit (tuning knob) */
+	int coop = anni_grid_blocks(grad_dtype, state_dtype, 1);
+	int split = anni_grid_blocks(grad_dtype, state_dtype, 0);
+	int dev = 0;
+	int sms = 0;
+
+	if (coop < 1 || split < 1)
+		return ANNI_E_CUDA;
+	if (split < coop)
+		coop = split;
+	if (e && atoi(e) > 0 && cudaGetDevice(&dev) == cudaSuccess
+	    && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess
+	    && sms > 0 && atoi(e) * sms < coop)
+		coop = atoi(e) * sms;
+	if (blocks)
+		*blocks = coop;
+	if (sc_log2)
+		*sc_log2 = superchunk_log2();
+	return ANNI_OK;
 }
 
 static int check_cfg(const anni_optstep_config *c)
@@ -117,6 +173,8 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 	    || cudaMalloc((void **)&h->d_seg_flags, (size_t)h->n_seg * sizeof(uint32_t)) != cudaSuccess
 	    || cudaMalloc((void **)&h->d_amax, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
 	    || cudaMalloc((void **)&h->d_scale, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
+	    || cudaMalloc((void **)&h->d_seg_done, (size_t)h->n_seg * sizeof(uint32_t)) != cudaSuccess
+	    || cudaMemset(h->d_seg_done, 0, (size_t)h->n_seg * sizeof(uint32_t)) != cudaSuccess
 	    || cudaMemset(h->ctl, 0, sizeof(anni_control)) != cudaSuccess
 	    || cudaMemset(h->d_amax, 0, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
 	    || cudaMemset(h->d_scale, 0, (size_t)h->n_seg * sizeof(float)) != cudaSuccess
@@ -127,26 +185,11 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 		anni_optstep_destroy(h);
 		return ANNI_E_CUDA;
 	}
-	h->blocks_coop = anni_grid_blocks(cfg->grad_dtype, cfg->state_dtype, 1);
-	h->blocks_split = anni_grid_blocks(cfg->grad_dtype, cfg->state_dtype, 0);
-	if (h->blocks_coop < 1 || h->blocks_split < 1) {
+	if (anni_engine_geometry(cfg->grad_dtype, cfg->state_dtype, &h->blocks_coop, &h->la.sc_log2) != ANNI_OK) {
 		anni_optstep_destroy(h);
 		return ANNI_E_CUDA;
 	}
-	/* same geometry for both forms: identical block partials, identical norm bits */
-	if (h->blocks_split > h->blocks_coop)
-		h->blocks_split = h->blocks_coop;
-	else
-		h->blocks_coop = h->blocks_split;
-	{
-		/* ANNI_B200_BLOCKS_PER_SM=k: fewer resident blocks than fit (tuning knob) */
-		const char *e = getenv("ANNI_B200_BLOCKS_PER_SM");
-		int sms = 0;
-
-		if (e && atoi(e) > 0 && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount,
-		    h->device) == cudaSuccess && sms > 0 && atoi(e) * sms < h->blocks_coop)
-			h->blocks_coop = h->blocks_split = atoi(e) * sms;
-	}
+	h->blocks_split = h->blocks_coop;
 	h->blocks_rn = h->blocks_split;
 	{
 		/* ANNI_B200_RN_BLOCKS_PER_SM=k: resident blocks of the reduce-scatter + norm kernel (tuning knob) */
@@ -163,9 +206,20 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 	h->la.seg_flags = h->d_seg_flags;
 	h->la.seg_amax = h->d_amax;
 	h->la.seg_scale = h->d_scale;
+	h->la.seg_done = h->d_seg_done;
 	h->la.n_seg = h->n_seg;
 	h->la.ctl = h->ctl;
-	h->la.sc_log2 = superchunk_log2();
+	{
+		/* ANNI_B200_FP8_PIPE=0: the older form, a whole-arena quantise phase after a second grid barrier */
+		const char *e = getenv("ANNI_B200_FP8_PIPE");
+
+		h->fp8_pipe = !(e && e[0] == '0');
+		/* ANNI_B200_FP8_LAG=k: rounds of the grid between leaving a tensor and quantising it (tuning knob) */
+		e = getenv("ANNI_B200_FP8_LAG");
+		h->la.pipe_lag = e && atoi(e) > 0 ? atoi(e) : ANNI_PIPE_LAG;
+		e = getenv("ANNI_B200_FP8_STREAM");
+		h->fp8_stream = e && e[0] == '1';
+	}
 	*out = h;
 	return ANNI_OK;
 }
@@ -179,6 +233,7 @@ extern "C" void anni_optstep_destroy(anni_optstep *h)
 	cudaFree(h->d_seg_flags);
 	cudaFree(h->d_amax);
 	cudaFree(h->d_scale);
+	cudaFree(h->d_seg_done);
 	cudaFree(h->d_aux);
 	cudaFree(h->d_tile_prefix);
 	free(h->h_seg_off);
@@ -229,11 +284,20 @@ extern "C" int anni_optstep_step(anni_optstep *h, const anni_optstep_hyper *hp, 
 
 	if (rc != ANNI_OK)
 		return rc;
-	if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
+	if (h->has_fp8 && h->fp8_pipe)
+		la.flags |= ANNI_LAUNCH_FP8_PIPE | (h->fp8_stream ? ANNI_LAUNCH_PIPE_STREAM : 0);	/* the kernel clears amax and counters itself: ONE launch */
+	else if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
 	    != cudaSuccess)
 		return ANNI_E_CUDA;
-	rc = anni_launch_fused(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_coop, st);
-	return rc != ANNI_OK ? rc : derived_after_step(h, &la, st);
+	{
+		const int slot = anni_op_begin(ANNI_OP_ADAM, st);
+
+		rc = anni_launch_fused(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_coop, st);
+		if (rc == ANNI_OK)
+			rc = derived_after_step(h, &la, st);
+		anni_op_end(slot, st);
+	}
+	return rc;
 }
 
 extern "C" int anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
@@ -243,7 +307,13 @@ extern "C" int anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, 
 
 	if (rc != ANNI_OK)
 		return rc;
-	return anni_launch_norm(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, (cudaStream_t)stream);
+	{
+		const int slot = anni_op_begin(ANNI_OP_SUMSQ, stream);
+
+		rc = anni_launch_norm(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, (cudaStream_t)stream);
+		anni_op_end(slot, stream);
+	}
+	return rc;
 }
 
 extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
@@ -257,7 +327,33 @@ extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp
 	if (h->has_fp8 && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st)
 	    != cudaSuccess)
 		return ANNI_E_CUDA;
-	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+	use_grad_arena(h, &la);
+	{
+		const int slot = anni_op_begin(ANNI_OP_ADAM, st);
+
+		rc = anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+		if (rc == ANNI_OK)
+			rc = zero_arena_tail(h, &la, st);
+		anni_op_end(slot, st);
+	}
+	return rc;
+}
+
+extern "C" int anni_optstep_step_with_sumsq(anni_optstep *h, const anni_optstep_hyper *hp,
+	const double *d_sumsq, void *stream)
+{
+	cudaStream_t st = (cudaStream_t)stream;
+	int rc;
+
+	if (!h || !hp || !d_sumsq || !h->bound)
+		return ANNI_E_ARG;
+	if (cudaMemcpyAsync(anni_optstep_reduce_buffer(h), d_sumsq, 2 * sizeof(double), cudaMemcpyDeviceToDevice,
+	    st) != cudaSuccess)
+		return ANNI_E_CUDA;
+	rc = anni_optstep_update(h, hp, stream);
+	if (rc == ANNI_OK && h->has_fp8)
+		rc = anni_optstep_quantize(h, stream);
+	return rc;
 }
 
 extern "C" int anni_optstep_set_derived(anni_optstep *h, const anni_seg_derived *aux, void *qkv_packed,
@@ -388,6 +484,49 @@ extern "C" int anni_optstep_set_multicast(anni_optstep *h, const void *mc_grad, 
 	return ANNI_OK;
 }
 
+extern "C" int anni_optstep_rotate_peers(anni_optstep *h, int first)
+{
+	const void *g[ANNI_MAX_PEERS];
+	uint16_t *t[ANNI_MAX_PEERS];
+	uint8_t *t8[ANNI_MAX_PEERS];
+	const int np = h ? h->la.n_peers : 0;
+	int k;
+
+	if (!h || np < 1 || first < 0 || first >= np)
+		return ANNI_E_ARG;
+	for (k = 0; k < np; k++) {
+		g[k] = h->la.peer_grad[(first + k) % np];
+		t[k] = h->la.twin_peer[(first + k) % np];
+		t8[k] = h->la.twin8_peer[(first + k) % np];
+	}
+	for (k = 0; k < np; k++) {
+		h->la.peer_grad[k] = g[k];
+		h->la.twin_peer[k] = t[k];
+		h->la.twin8_peer[k] = t8[k];
+	}
+	return ANNI_OK;
+}
+
+extern "C" int anni_optstep_set_grad_arena(anni_optstep *h, void *arena, uint64_t stride, int parts)
+{
+	if (!h)
+		return ANNI_E_ARG;
+	if (!arena) {
+		h->grad_arena = NULL;
+		h->grad_arena_stride = 0;
+		h->grad_arena_parts = 0;
+		return ANNI_OK;
+	}
+	/* every part must hold this shard, and vector stores need part bases that keep 16-byte alignment */
+	if (parts < 1 || parts > ANNI_MAX_PEERS || stride < h->cfg.shard_n || (stride & 7u) != 0
+	    || ((uintptr_t)arena & 15) != 0)
+		return ANNI_E_ARG;
+	h->grad_arena = arena;
+	h->grad_arena_stride = stride;
+	h->grad_arena_parts = parts;
+	return ANNI_OK;
+}
+
 extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream)
 {
 	anni_launch la;
@@ -425,6 +564,8 @@ static int restrict_range(const anni_optstep *h, anni_launch *la, uint64_t off, 
 		if (la->twin8_peer[k])
 			la->twin8_peer[k] += off;
 	}
+	if (la->zero_base)
+		la->zero_base = (char *)la->zero_base + off * gsz;
 	if (la->mc_grad)
 		la->mc_grad = (const char *)la->mc_grad + off * gsz;
 	if (la->mc_twin)
@@ -463,6 +604,7 @@ extern "C" int anni_optstep_update_range(anni_optstep *h, const anni_optstep_hyp
 		return rc;
 	if (la.seg_aux)
 		return ANNI_E_ARG;	/* derived twins are a whole-arena, one-GPU feature */
+	use_grad_arena(h, &la);
 	rc = restrict_range(h, &la, elem_off, elem_n);
 	if (rc != ANNI_OK)
 		return rc;
@@ -476,7 +618,10 @@ extern "C" int anni_optstep_update_range(anni_optstep *h, const anni_optstep_hyp
 	if ((flags & ANNI_RANGE_FIRST) && h->has_fp8
 	    && cudaMemsetAsync(h->d_amax, 0, (size_t)h->n_seg * sizeof(float), st) != cudaSuccess)
 		return ANNI_E_CUDA;
-	return anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+	rc = anni_launch_update(&la, h->cfg.grad_dtype, h->cfg.state_dtype, h->blocks_split, st);
+	if (rc != ANNI_OK || !(flags & ANNI_RANGE_LAST))
+		return rc;
+	return zero_arena_tail(h, &la, st);
 }
 
 extern "C" int anni_peer_copy(void *dst, const void *src, size_t nbytes, void *stream)
@@ -585,6 +730,20 @@ extern "C" int anni_optstep_loss_scale_init(anni_optstep *h, double scale, int g
 	head.good_steps = 0;
 	return cudaMemcpy(h->ctl, &head, nb, cudaMemcpyHostToDevice) == cudaSuccess
 	    ? ANNI_OK : ANNI_E_CUDA;
+}
+
+/* Polls the blocks of the one-launch fp8 step have spent waiting for each other since the last call (diagnostics). */
+extern "C" long long anni_optstep_pipe_polls(anni_optstep *h, void *stream)
+{
+	uint32_t v = 0;
+	const uint32_t zero = 0;
+	char *p = h ? (char *)h->ctl + offsetof(anni_control, pipe_polls) : NULL;
+
+	if (!h || cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess
+	    || cudaMemcpy(&v, p, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess
+	    || cudaMemcpy(p, &zero, sizeof(zero), cudaMemcpyHostToDevice) != cudaSuccess)
+		return -1;
+	return (long long)v;
 }
 
 extern "C" int anni_optstep_grid(anni_optstep *h, int *blocks, int *threads)

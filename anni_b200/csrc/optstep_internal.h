@@ -24,6 +24,32 @@
 #define ANNI_UVEC		4
 #define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
 #define ANNI_UCHUNK_LOG2	10
+/*
+** How the float -> double widenings are shared between the conversion unit (16 per clock and
+** SM on B200, also busy with square roots, reciprocals and the narrowing conversions) and the
+** integer pipe (see widen_alu in optstep.cu).  Results do not depend on these.
+**   ANNI_NORM_ALU_LANES  of the eight gradients of a vector, how many the norm phase widens
+**                        with integer instructions
+**   ANNI_WIDEN_FAST / ANNI_WIDEN_EXACT  bit 0: gradient, 1: m, 2: v, 3: master -- widened
+**                        with integer instructions in the fast / exact update
+**   ANNI_EXACT_SPLIT     exact update: take the rounded moments' doubles from a Veltkamp split
+**                        instead of converting the stored floats back
+*/
+#ifndef ANNI_NORM_ALU_LANES
+#define ANNI_NORM_ALU_LANES	0
+#endif
+#ifndef ANNI_WIDEN_FAST
+#define ANNI_WIDEN_FAST		0
+#endif
+#ifndef ANNI_WIDEN_EXACT
+#define ANNI_WIDEN_EXACT	0
+#endif
+#ifndef ANNI_PIPE_LAG
+#define ANNI_PIPE_LAG		1	/* default of anni_launch.pipe_lag */
+#endif
+#ifndef ANNI_EXACT_SPLIT
+#define ANNI_EXACT_SPLIT	1
+#endif
 /* tile of the transposed e4m3 twins: rows x columns of the master (kernel and host tile count) */
 #define ANNI_TT_R		128
 #define ANNI_TT_C		64
@@ -53,6 +79,7 @@ typedef struct anni_control {
 	uint32_t	bar_count;	/* arrivals at the in-kernel barriers; reset by the last block */
 	uint32_t	norm_ticket;	/* blocks that finished the norm kernel */
 	uint32_t	done_ticket;	/* blocks that finished the update */
+	uint32_t	pipe_polls;	/* polls spent waiting for other blocks' tensors (one-launch fp8 step) */
 	double		partials[ANNI_MAX_BLOCKS];
 } anni_control;
 
@@ -70,6 +97,7 @@ typedef struct anni_launch {
 	const uint32_t	*seg_flags;	/* device, n_seg */
 	float		*seg_amax;	/* device, n_seg */
 	float		*seg_scale;	/* device, n_seg */
+	uint32_t	*seg_done;	/* device, n_seg: blocks that have finished updating each tensor (one-launch fp8 step) */
 	const anni_seg_derived *seg_aux;	/* device, n_seg, or NULL: shapes and targets of the derived twins */
 	uint16_t	*qkv_packed;	/* [Wq|Wk|Wv] bf16 matrices, one per layer */
 	uint8_t		*fp8_t;		/* transposed e4m3 twins */
@@ -77,6 +105,7 @@ typedef struct anni_launch {
 	int		flags;		/* ANNI_STEP_* | ANNI_LAUNCH_* */
 	int		aligned;	/* every buffer 16-byte aligned: vector path allowed */
 	int		sc_log2;	/* log2 of the chunks per super-chunk (see walk_chunk) */
+	int		pipe_lag;	/* one-launch fp8 step: rounds of the grid between leaving a tensor and quantising it */
 	double		grad_scale;
 	double		clip;
 	double		b1;
@@ -113,6 +142,17 @@ typedef struct anni_launch {
 	const void	*mc_grad;
 	uint16_t	*mc_twin;
 	uint8_t		*mc_twin8;
+	/*
+	** ZeRO-1, "the step leaves the gradients zeroed" (lang/lm_adam.c:597 of the reference): the
+	** buffer the backward pass accumulates into is this rank's FULL gradient arena, of which the
+	** update only ever sees the reduced shard.  zero_base = the arena at the element that stands
+	** for shard element 0 of part 0, zero_stride = elements per part, zero_parts = parts (world
+	** size): the update then clears element e of every part where it would have cleared
+	** grad[e].  NULL / 0: clear the bound gradient buffer itself (one GPU).
+	*/
+	void		*zero_base;
+	uint64_t	zero_stride;
+	int		zero_parts;
 	anni_control	*ctl;
 } anni_launch;
 
@@ -122,6 +162,8 @@ typedef struct anni_launch {
 #define ANNI_LAUNCH_HAS_FP8	0x400	/* some segment asks for an e4m3 twin */
 #define ANNI_LAUNCH_ACCUMULATE	0x800	/* norm over a part of the shard: add to the running sum */
 #define ANNI_LAUNCH_NO_EPILOGUE	0x1000	/* update over a part of the shard that is not the last: the step stays open */
+#define ANNI_LAUNCH_PIPE_STREAM	0x4000	/* ... and store those tensors' masters with the streaming hint all the same (tuning) */
+#define ANNI_LAUNCH_FP8_PIPE	0x2000	/* one-launch step: quantise tensor by tensor behind the update (see update_phase) */
 
 #ifdef __cplusplus
 extern "C" {
@@ -142,13 +184,26 @@ int	anni_launch_quantize_transposed(const anni_launch *a, const int64_t *tile_pr
 		int blocks, cudaStream_t st);
 int	anni_launch_barrier_timeout(anni_control *ctl, int blocks, unsigned max_polls, cudaStream_t st);
 int	anni_launch_reduce_norm(const anni_launch *a, int grad_dtype, int blocks, cudaStream_t st);
+/* clears elements [from, stride) of every part of a gradient arena (see anni_launch.zero_base) */
+int	anni_launch_zero_tail(void *arena, int grad_dtype, uint64_t from, uint64_t stride, int parts,
+		cudaStream_t st);
 int	anni_launch_f32_to_bf16(uint16_t *dst, const float *src, uint64_t n, cudaStream_t st);
 int	anni_launch_axpy(float *y, const float *x, float a, uint64_t n, cudaStream_t st);
 /* Persistent-grid size for the given kernel family on the current device. */
 int	anni_grid_blocks(int grad_dtype, int state_dtype, int cooperative);
+/* Grid and super-chunk size every launcher of the step kernels uses (tuning knobs applied). */
+int	anni_engine_geometry(int grad_dtype, int state_dtype, int *blocks, int *sc_log2);
 /* Fills the hyper-parameter part of a launch; ANNI_E_ARG on values the reference rejects. */
 int	anni_fill_hyper(anni_launch *a, const anni_optstep_hyper *hp);
 void	anni_count_launch(void);
+
+/* ANN_OP_PROF event pairs (gpu_compat.cu): begin returns a slot (or -1: profiling off), end closes it */
+enum { ANNI_OP_ADAM, ANNI_OP_SUMSQ, ANNI_OP_COLSUM, ANNI_OP_AXPY, ANNI_OP_CONVERT, ANNI_OP_N };
+int	anni_op_begin(int op, void *stream);
+void	anni_op_end(int slot, void *stream);
+/* host gradient vector -> its slice of a device gradient flat (see gpu_mat_col_sum_add) */
+int	anni_colsum_register(const float *host, float *dev, int cols);
+void	anni_colsum_forget(const void *dev_lo, const void *dev_hi);
 
 #ifdef __cplusplus
 }

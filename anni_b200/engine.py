@@ -164,7 +164,7 @@ class OptStep:
     """
 
     def __init__(self, segments: Optional[Segments], *, n_arena=None, grad_dtype=DT_BF16,
-                 state_dtype=DT_F32, shard_off=0, shard_n=None, device="cuda"):
+                 state_dtype=DT_F32, shard_off=0, shard_n=None, device="cuda", handle=None):
         if not torch.cuda.is_available():
             raise RuntimeError("anni_b200 needs a CUDA device: there is no CPU path")
         self.L = capi.lib()
@@ -174,6 +174,14 @@ class OptStep:
         self.shard_off = int(shard_off)
         self.shard_n = int(self.n_arena - self.shard_off if shard_n is None else shard_n)
         self.grad_dtype, self.state_dtype = grad_dtype, state_dtype
+        self.master = self.m = self.v = self.grad = self.twin_bf16 = self.twin_fp8 = None
+        self.owned = handle is None
+        if handle is not None:
+            # an engine that something else created and will destroy (the C ZeRO-1 driver's)
+            self.h = C.c_void_p(handle)
+            self.n_seg = len(segments) if segments is not None and len(segments) > 0 else 1
+            self.has_fp8 = bool(segments is not None and (segments.flag_array & SEG_TWIN_FP8).any())
+            return
         cfg = capi.Config()
         cfg.n_arena, cfg.shard_off, cfg.shard_n = self.n_arena, self.shard_off, self.shard_n
         cfg.grad_dtype, cfg.state_dtype = grad_dtype, state_dtype
@@ -193,7 +201,6 @@ class OptStep:
         with torch.cuda.device(self.device):
             check("anni_optstep_create", self.L.anni_optstep_create(C.byref(cfg), C.byref(h)))
         self.h = h
-        self.master = self.m = self.v = self.grad = self.twin_bf16 = self.twin_fp8 = None
 
     # -- memory -----------------------------------------------------------------------
     def allocate(self, twin_bf16=True, pad_to=None):
@@ -250,6 +257,13 @@ class OptStep:
     def update(self, hp, stream=None):
         check("anni_optstep_update", self.L.anni_optstep_update(self.h, C.byref(hp), self._stream(stream)))
 
+    def step_with_sumsq(self, hp, sumsq, stream=None):
+        """The step without its norm pass: ``sumsq`` is a device float64 tensor {sum of squares of
+        the raw gradients, non-finite count} supplied by whoever produced the gradients."""
+        assert sumsq.is_cuda and sumsq.dtype == torch.float64 and sumsq.numel() >= 2
+        check("anni_optstep_step_with_sumsq",
+              self.L.anni_optstep_step_with_sumsq(self.h, C.byref(hp), sumsq.data_ptr(), self._stream(stream)))
+
     def set_derived(self, aux, qkv_packed=None, fp8_t=None):
         """Derived twins emitted by the step: ``aux`` is a list of capi.SegDerived (one per tensor),
         ``qkv_packed`` a bf16 tensor for the packed [Wq|Wk|Wv] matrices, ``fp8_t`` a uint8 tensor
@@ -275,6 +289,18 @@ class OptStep:
         check("anni_optstep_set_multicast",
               self.L.anni_optstep_set_multicast(self.h, v(mc_grad), v(mc_twin), v(mc_twin_fp8),
                                                 int(arena_off_padded)))
+
+    def rotate_peers(self, first):
+        """Visit the peers starting at index ``first`` (see anni_optstep_rotate_peers)."""
+        check("anni_optstep_rotate_peers", self.L.anni_optstep_rotate_peers(self.h, int(first)))
+
+    def set_grad_arena(self, arena, stride, parts):
+        """ZeRO-1: the rank's full gradient arena (a tensor, or None) that ``update`` clears in
+        place of the bound shard buffer (see anni_optstep_set_grad_arena)."""
+        self._grad_arena = arena
+        check("anni_optstep_set_grad_arena",
+              self.L.anni_optstep_set_grad_arena(self.h, arena.data_ptr() if arena is not None else None,
+                                                 int(stride), int(parts)))
 
     def reduce_norm(self, hp, stream=None):
         check("anni_optstep_reduce_norm",
@@ -352,7 +378,8 @@ class OptStep:
 
     def close(self):
         if getattr(self, "h", None):
-            self.L.anni_optstep_destroy(self.h)
+            if self.owned:
+                self.L.anni_optstep_destroy(self.h)
             self.h = None
 
     def __del__(self):

@@ -59,6 +59,8 @@ the issuing GPU, so its own shard travels out and back over its link -- the busy
 carries the whole arena instead of (N-1)/N of it.  Measured at N = 2: 3.46 ms per step against
 2.09 ms with plain peer loads / stores.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -98,7 +100,12 @@ class Zero1:
         self.per, own = shard_geometry(self.n_arena, self.world)
         self.shard_off, self.shard_n = own[self.rank]
         self.padded = self.per * self.world
-        if make_stepper is None:
+        self._c = None
+        self._comm = None
+        self._shard_n_real = self.shard_n
+        has_fp8 = bool((segments.flag_array & 4).any()) if len(segments) else False
+        default_stepper = make_stepper is None
+        if default_stepper:
             from .engine import OptStep
             dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
 
@@ -108,41 +115,34 @@ class Zero1:
             self.device = dev
         else:
             self.device = torch.device("cpu") if device is None else device
-        # an empty shard still takes part in every collective; it sits at the arena end
-        self.eng = make_stepper(min(self.shard_off, self.n_arena), self.shard_n)
         gdt, sdt, dev = _TORCH_DT[grad_dtype], _TORCH_DT[state_dtype], self.device
         self._gdt = gdt
         self._arenas = []
         if peer is None:
-            peer = self.world > 1 and dev.type == "cuda" and hasattr(self.eng, "set_peers")
+            peer = self.world > 1 and dev.type == "cuda" and default_stepper
         self.copy_mode = peer == "copy" and self.world > 1
         self.peer = bool(peer) and self.world > 1
         self.multicast = bool(multicast)        # use NVSwitch multicast addresses when the arenas have them
+        # several ranks on GPUs: the step sequence itself runs in the library (anni_zero1_step, the
+        # call a C trainer makes); this class then only owns the memory.  ANNI_B200_ZERO1_DRIVER=py
+        # keeps the sequence below in Python (what copy mode and the CPU stand-in always use).
+        use_c = (default_stepper and dev.type == "cuda" and self.world > 1 and not self.copy_mode
+                 and os.environ.get("ANNI_B200_ZERO1_DRIVER", "c") != "py")
+        if use_c:
+            from . import capi
+            use_c = bool(capi.lib().anni_zero1_nccl_available())
         self._tiny = torch.zeros(1, dtype=torch.float32, device=dev)
         if self.peer:
             self.grad_full, self._peer_grad = self._symm(self.padded, gdt)
             self.twin_full, self._peer_twin = self._symm(self.padded, torch.bfloat16)
-            if self.eng.has_fp8:
+            if has_fp8:
                 self.twin8_full, self._peer_twin8 = self._symm(self.padded, torch.uint8)
             else:
                 self.twin8_full, self._peer_twin8 = None, None
-            if self.copy_mode:
-                # local landing area for the peers' copies of this shard, and a stream for the copies
-                self._stage = torch.zeros(self.world, self.per, dtype=gdt, device=dev)
-                # one stream per peer, so that the copies to / from all peers run at the same time
-                self._copy_streams = [torch.cuda.Stream(device=dev) for _ in range(self.world - 1)]
-                n_parts = copy_parts if copy_parts else (4 if self.shard_n >= (4 << 20) else 1)
-                step = -(-max(self.shard_n, 1) // n_parts)
-                step = -(-step // SHARD_ALIGN) * SHARD_ALIGN
-                self._parts = [(o, min(step, self.shard_n - o)) for o in range(0, max(self.shard_n, 1), step)]
-                if self.shard_n == 0:
-                    self._parts = [(0, 0)]
-            self._attach_peers()
         else:
             self.grad_full = self._local_grad_arena()
             self.twin_full = torch.zeros(self.padded, dtype=torch.bfloat16, device=dev)
-            self.twin8_full = (torch.zeros(self.padded, dtype=torch.uint8, device=dev)
-                               if self.eng.has_fp8 else None)
+            self.twin8_full = torch.zeros(self.padded, dtype=torch.uint8, device=dev) if has_fp8 else None
         lo, hi = self.rank * self.per, (self.rank + 1) * self.per
         self.master = torch.zeros(self.per, dtype=torch.float32, device=dev)
         self.m = torch.zeros(self.per, dtype=sdt, device=dev)
@@ -152,9 +152,94 @@ class Zero1:
                            else torch.zeros(self.per, dtype=gdt, device=dev))
         self.twin_shard = self.twin_full[lo:hi]
         self.twin8_shard = self.twin8_full[lo:hi] if self.twin8_full is not None else None
-        self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard,
-                      self.twin8_shard)
+        if use_c:
+            self._create_c_driver(grad_dtype, state_dtype)
+        else:
+            # an empty shard still takes part in every collective; it sits at the arena end
+            self.eng = make_stepper(min(self.shard_off, self.n_arena), self.shard_n)
+            if self.peer:
+                if self.copy_mode:
+                    # local landing area for the peers' copies of this shard, and a stream for the copies
+                    self._stage = torch.zeros(self.world, self.per, dtype=gdt, device=dev)
+                    # one stream per peer, so that the copies to / from all peers run at the same time
+                    self._copy_streams = [torch.cuda.Stream(device=dev) for _ in range(self.world - 1)]
+                    n_parts = copy_parts if copy_parts else (4 if self.shard_n >= (4 << 20) else 1)
+                    step = -(-max(self.shard_n, 1) // n_parts)
+                    step = -(-step // SHARD_ALIGN) * SHARD_ALIGN
+                    self._parts = [(o, min(step, self.shard_n - o)) for o in range(0, max(self.shard_n, 1), step)]
+                    if self.shard_n == 0:
+                        self._parts = [(0, 0)]
+                self._attach_peers()
+            self.eng.bind(self.master, self.m, self.v, self.grad_shard, self.twin_shard,
+                          self.twin8_shard)
+            self._name_grad_arena()
         self.timing = None
+
+    # -- the library's own driver of the sequence (include/anni_zero1.h) -------------------------
+    def _ptr_array(self, ptrs):
+        import ctypes as C
+        return (C.c_void_p * len(ptrs))(*[C.c_void_p(int(p)) for p in ptrs])
+
+    def _create_c_driver(self, grad_dtype, state_dtype):
+        import ctypes as C
+        import numpy as np
+        from . import capi
+        from .engine import OptStep
+        L = capi.lib()
+        # a communicator of the library's own: rank 0 draws the id, the process group carries it
+        box = [None]
+        if self.rank == 0:
+            raw = (C.c_char * capi.ZERO1_UNIQUE_ID_BYTES)()
+            capi.check("anni_zero1_unique_id", L.anni_zero1_unique_id(raw))
+            box[0] = bytes(raw)
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                                   group=self.group)
+        comm = C.c_void_p()
+        with torch.cuda.device(self.device):
+            capi.check("anni_zero1_comm_init", L.anni_zero1_comm_init(box[0], self.rank, self.world, C.byref(comm)))
+        self._comm = comm
+        cfg = capi.Zero1Config()
+        self._c_off = np.ascontiguousarray(self.segments.offsets)
+        self._c_flg = np.ascontiguousarray(self.segments.flag_array)
+        cfg.n_arena, cfg.grad_dtype, cfg.state_dtype = self.n_arena, grad_dtype, state_dtype
+        cfg.n_seg, cfg.seg_off, cfg.seg_flags = len(self.segments), self._c_off.ctypes.data, self._c_flg.ctypes.data
+        cfg.rank, cfg.world, cfg.nccl_comm = self.rank, self.world, comm
+        cfg.grad_arena, cfg.twin_arena = self.grad_full.data_ptr(), self.twin_full.data_ptr()
+        cfg.twin_fp8_arena = self.twin8_full.data_ptr() if self.twin8_full is not None else None
+        keep = []
+        self.uses_multicast = False
+        if self.peer:
+            pg, pt, p8 = self._peer_grad, self._peer_twin, self._peer_twin8
+            keep = [self._ptr_array(pg[0]), self._ptr_array(pt[0]), self._ptr_array(p8[0]) if p8 else None]
+            cfg.peer_grad = C.cast(keep[0], C.c_void_p)
+            cfg.peer_twin = C.cast(keep[1], C.c_void_p)
+            cfg.peer_twin_fp8 = C.cast(keep[2], C.c_void_p) if p8 else None
+            self.uses_multicast = bool(pg[1] and pt[1] and (p8 is None or p8[1]))
+            if self.uses_multicast:
+                cfg.mc_grad, cfg.mc_twin = pg[1], pt[1]
+                cfg.mc_twin_fp8 = p8[1] if p8 else None
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            capi.check("anni_zero1_create", L.anni_zero1_create(C.byref(cfg), C.byref(h)))
+        self._c, self._c_keep = h, keep
+        capi.check("anni_zero1_bind", L.anni_zero1_bind(h, self.master.data_ptr(), self.m.data_ptr(),
+                                                        self.v.data_ptr(), self.grad_shard.data_ptr()))
+        self.eng = OptStep(self.segments, grad_dtype=grad_dtype, state_dtype=state_dtype,
+                           shard_off=min(self.shard_off, self.n_arena), shard_n=self.shard_n,
+                           device=self.device, handle=L.anni_zero1_engine(h))
+        self.eng.master, self.eng.m, self.eng.v, self.eng.grad = self.master, self.m, self.v, self.grad_shard
+        self.eng.twin_bf16, self.eng.twin_fp8 = self.twin_shard, self.twin8_shard
+        self._arena_by_engine = True
+
+    def close(self):
+        """Releases the library-side driver and its communicator (collective when there is one)."""
+        if self._c is not None:
+            from . import capi
+            torch.cuda.synchronize(self.device)
+            self.eng.close()
+            capi.lib().anni_zero1_destroy(self._c)
+            capi.lib().anni_zero1_comm_free(self._comm)
+            self._c = self._comm = None
 
     # -- peer memory ----------------------------------------------------------------------
     def _symm(self, n, dtype):
@@ -180,9 +265,27 @@ class Zero1:
             self.uses_multicast = False
             return
         self.eng.set_peers(pg[0], pt[0], p8[0] if p8 else None, off)
+        if os.environ.get("ANNI_B200_PEER_ROTATE", "1") != "0":
+            # remote copies first, each rank starting at another peer; this rank's own copy last
+            self.eng.rotate_peers((self.rank + 1) % self.world)
         self.uses_multicast = bool(pg[1] and pt[1] and (p8 is None or p8[1]))
         if self.uses_multicast:
             self.eng.set_multicast(pg[1], pt[1], p8[1] if p8 else 0, off)
+
+    def _name_grad_arena(self):
+        """Several ranks: the buffer the backward pass accumulates into is the FULL arena, of which
+        the update only sees the reduced shard -- tell the engine, so that "the step leaves the
+        gradients zeroed" (lang/lm_adam.c:597 of the reference) holds for it: the update kernel
+        clears the whole local arena once every peer has read it.  A stepper without that call
+        (the CPU stand-in of the tests) gets the arena cleared after its update."""
+        self._arena_by_engine = False
+        if self.world > 1 and hasattr(self.eng, "set_grad_arena"):
+            self.eng.set_grad_arena(self.grad_full, self.per, self.world)
+            self._arena_by_engine = True
+
+    def _zero_arena_after_update(self, hp):
+        if self.world > 1 and not self._arena_by_engine and (getattr(hp, "flags", 2) & 2):
+            self.grad_full.zero_()
 
     def _local_grad_arena(self):
         """A zeroed gradient arena in this GPU's memory: on one GPU compressible memory where the
@@ -210,6 +313,19 @@ class Zero1:
         """Make (tensor, peer pointers) from new_grad_arena the input of the next steps."""
         t, ptrs = arena
         self.grad_full = t
+        if self._c is not None:
+            from . import capi
+            if self.peer:
+                self._peer_grad = ptrs
+                self._c_keep[0] = self._ptr_array(ptrs[0])
+                arr, mc = self._c_keep[0], (ptrs[1] if self.uses_multicast else None)
+            else:
+                arr, mc = None, None
+            capi.check("anni_zero1_set_grad_arena",
+                       capi.lib().anni_zero1_set_grad_arena(self._c, t.data_ptr(), arr, mc))
+            return
+        if self.world > 1:
+            self._name_grad_arena()
         if self.peer:
             self._peer_grad = ptrs
             self._attach_peers()
@@ -322,11 +438,26 @@ class Zero1:
         return t, epoch, step
 
     # -- the step ------------------------------------------------------------------------
-    def step(self, hp, record=None, grads_complete=False):
-        """One sharded step.  ``record`` (optional) is called with a phase name after each
-        phase has been queued, so a caller can drop timing events between them.
-        ``grads_complete``: every rank's gradient arena was complete before the previous
-        step's closing barrier (peer mode then skips the opening barrier)."""
+    PHASES = ("reduce_scatter+norm", "all_reduce", "update+all_gather", "barrier")
+
+    def step(self, hp, record=None, grads_complete=False, phase_events=None):
+        """One sharded step.  ``grads_complete``: every rank's gradient arena was complete before
+        the previous step's closing barrier (peer mode then skips the opening barrier).
+        Timing hooks: ``phase_events``, four ``torch.cuda.Event`` (timing enabled and recorded
+        once before, so that they exist) which the library records after the phases named in
+        ``PHASES`` when the sequence runs there (``driver == "library"``); ``record``, a callable
+        given a phase name after each phase has been queued, when it runs in Python."""
+        if self._c is not None:
+            from . import capi
+            import ctypes as C
+            evs = None
+            if phase_events is not None:
+                evs = (C.c_void_p * 4)(*[C.c_void_p(int(e.cuda_event)) for e in phase_events])
+            st = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            capi.check("anni_zero1_step",
+                       capi.lib().anni_zero1_step(self._c, C.byref(hp),
+                                                  capi.ZERO1_GRADS_COMPLETE if grads_complete else 0, st, evs))
+            return
         mark = record if record is not None else (lambda name: None)
         if self.world == 1 and hasattr(self.eng, "step"):
             self.eng.step(hp)           # nothing to exchange: the single cooperative launch
@@ -342,7 +473,8 @@ class Zero1:
             mark("reduce_scatter+norm")
             dist.all_reduce(self.eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)
             mark("all_reduce")
-            self.eng.update(hp)
+            self.eng.update(hp)         # also clears this rank's gradient arena: every peer has read it
+            self._zero_arena_after_update(hp)
             if self.eng.has_fp8:
                 dist.all_reduce(self.eng.amax_tensor(), op=dist.ReduceOp.MAX, group=self.group)
                 self.eng.quantize()
@@ -358,7 +490,8 @@ class Zero1:
         if self.world > 1:
             dist.all_reduce(self.eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)
         mark("norm")
-        self.eng.update(hp)
+        self.eng.update(hp)             # several ranks: clears the full arena the reduce-scatter has consumed
+        self._zero_arena_after_update(hp)
         if self.eng.has_fp8:
             if self.world > 1:
                 dist.all_reduce(self.eng.amax_tensor(), op=dist.ReduceOp.MAX, group=self.group)
@@ -399,7 +532,7 @@ class Zero1:
         mark("all_reduce")
         last = len(self._parts) - 1
         for i, (o, n) in enumerate(self._parts):
-            eng.update_range(hp, o, n, first=i == 0, last=i == last, local_twins=True)
+            eng.update_range(hp, o, n, first=i == 0, last=i == last, local_twins=True)   # + clears the arena part
             for k, cs in zip(others, streams):
                 after(main, cs)
                 eng.peer_copy(pt[k] + (base + o) * 2, self.twin_full.data_ptr() + (base + o) * 2, n * 2, cs)
@@ -414,6 +547,11 @@ class Zero1:
         mark("update+all_gather")
         self._barrier()
         mark("barrier")
+
+    @property
+    def driver(self):
+        """Where the step sequence runs: "library" (anni_zero1_step) or "python"."""
+        return "library" if self._c is not None else "python"
 
     def status(self):
         return self.eng.status()

@@ -18,6 +18,7 @@ timed on this host, bounded sample), `e2e` (same metric through the C ABI with H
 gradient buffers: pinned H2D copy + step + D2H status inside the timed region).
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -43,10 +44,10 @@ WORKLOADS = {
     "synth3b": ("synth3b", "bf16", "f32", "bf16", 28),           # configuration 4 (8 GPUs)
 }
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0)
-# DRAM bytes per parameter of the fused kernel from the ncu capture summarised in
-# profiles/fused_kernel_bf16state_100M.md (dram__bytes_read.sum + dram__bytes_write.sum of a
-# 100.7M-parameter launch; traffic grows in proportion to the parameter count).
-NCU_DRAM_BYTES_PER_PARAM = 21.54   # dram read + write of one fused launch / parameters (ncu, 100.7 M case, profiles/)
+# DRAM bytes per parameter of the fused kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
+# 100.7M-parameter launch captured with ncu, divided by the parameter count (traffic grows in
+# proportion to it).
+NCU_DRAM_BYTES_PER_PARAM = 21.54
 
 
 def measured_peaks():
@@ -85,7 +86,10 @@ class ClockSampler(threading.Thread):
         self.stop_flag = True
         if self.proc is not None:
             self.proc.terminate()
-        rows = [r for ts, r in self.rows if t0 - 0.2 <= ts <= t1 + 0.2] or [r for _, r in self.rows]
+        return self.window(t0, t1)
+
+    def window(self, t0, t1):
+        rows = [r for ts, r in list(self.rows) if t0 - 0.2 <= ts <= t1 + 0.2] or [r for _, r in list(self.rows)]
         sm, mx, reasons = [], [], set()
         for r in rows:
             try:
@@ -141,16 +145,73 @@ def cpu_reference_all_cores(ref, p, gsrc, steps):
                 note="one independent reference optimizer per host core, stepped concurrently")
 
 
-def cpu_reference_step_rate(sample, steps, warmup):
+def host_mem_available():
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    return 0
+
+
+def synthetic_host_arrays(sample):
+    """Weights N(0, 0.02) and gradients N(0, 5e-4) with 0.1 % of the entries x100, as fp32 host
+    arrays: 16 Mi fresh draws each, repeated to the requested length (the reference's loop does
+    the same arithmetic on every element whatever its value, and 64 MB is far beyond any cache)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    block = min(sample, 1 << 24)
+    pb = rng.standard_normal(block, dtype=np.float32) * np.float32(0.02)
+    gb = rng.standard_normal(block, dtype=np.float32) * np.float32(5e-4)
+    gb[rng.random(block, dtype=np.float32) < 1e-3] *= 100
+    p = np.empty(sample, np.float32)
+    g = np.empty(sample, np.float32)
+    for lo in range(0, sample, block):
+        hi = min(sample, lo + block)
+        p[lo:hi] = pb[:hi - lo]
+        g[lo:hi] = gb[:hi - lo]
+    return p, g
+
+
+def reference_sample_size(steps, warm, budget_s=None):
+    """The largest arena -- the whole 555M one if possible -- that the reference's host loop gets
+    through `steps + warm` times within the budget on this host.  Set-up (the reference's slot
+    table: 24 bytes per parameter, filled element by element) and step time per parameter are
+    measured on a 16 Mi-parameter probe first and taken to grow in proportion."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import RefLib
+    small = 32 << 20
+    if budget_s is None:        # seconds the whole reference run may take (ANNI_B200_REF_BUDGET_S overrides)
+        budget_s = float(os.environ.get("ANNI_B200_REF_BUDGET_S", "200"))
+    if not RefLib.available():
+        return small
+    n0 = 16 << 20
+    t0 = time.perf_counter()
+    p, g = synthetic_host_arrays(n0)
+    ref = RefLib()
+    h = ref.L.ref_adam_bench_create(p.ctypes.data, g.ctypes.data, n0, HYPER["beta1"], HYPER["beta2"],
+                                    HYPER["eps"], HYPER["wd"], HYPER["clip"], 999)
+    t1 = time.perf_counter()
+    ref.L.ref_adam_bench_step(h, HYPER["lr"], 1.0)
+    t2 = time.perf_counter()
+    ref.L.ref_adam_bench_free(h)
+    setup_pp, step_pp = (t1 - t0) / n0, (t2 - t1) / n0
+    avail = host_mem_available()
+    for sample in (N_PARAMS, 256 << 20, 128 << 20, 64 << 20):
+        if 48 * sample < avail and 1.5 * setup_pp * sample + (steps + warm) * step_pp * sample <= budget_s:
+            return sample
+    return small
+
+
+def cpu_reference_step_rate(sample, steps, warmup, all_cores=True):
     """params/s of lm_adam_step_scaled's host loop (the reference's object code when
     oracle/_ref/libannref.so exists, else this repository's C port), one thread."""
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle_lib import Oracle, RefLib
-    rng = np.random.default_rng(0)
-    p = rng.normal(0, 0.02, sample).astype(np.float32)
-    gsrc = rng.normal(0, 5e-4, sample).astype(np.float32)
-    gsrc[rng.random(sample) < 1e-3] *= 100
+    p, gsrc = synthetic_host_arrays(sample)
     g = gsrc.copy()
     times = []
     if RefLib.available():
@@ -181,7 +242,7 @@ def cpu_reference_step_rate(sample, steps, warmup):
                 times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
     extra = {}
-    if kind == "reference":
+    if kind == "reference" and all_cores:
         extra["all_cores"] = cpu_reference_all_cores(ref, p, gsrc, steps)
     return dict(value=sample / sec, unit="params/s", cores=cores, kind=kind, **extra,
                 sample=f"{sample} fp32 parameters of the {WORKLOAD} distribution, {len(times)} timed "
@@ -192,8 +253,11 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    sample = 32 * 1024 * 1024
-    base, sec = cpu_reference_step_rate(sample, max(1, args.steps), max(1, min(args.warmup, 3)))
+    # the whole 555M arena when the host has room for it and K + W steps of it end within a few
+    # minutes (about 5 s each on one core, after the set-up); otherwise the largest sample that does
+    steps, warm = max(1, args.steps), max(1, min(args.warmup, 5))
+    sample = reference_sample_size(steps, warm)
+    base, sec = cpu_reference_step_rate(sample, steps, warm, all_cores=False)
     line = {
         "impl": "reference", "metric": "adam_step_params_per_s", "value": base["value"],
         "unit": "params/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -201,8 +265,9 @@ def run_reference(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "n_params": N_PARAMS, "sample_params": sample,
-                   "note": "reference CPU host loop (double math, fp32 storage), single-threaded "
-                           "by construction; each step a bounded sample"},
+                   "note": "reference CPU host loop (double math, fp32 storage), single-threaded by "
+                           "construction; " + ("every step the whole arena" if sample == N_PARAMS
+                                               else "each step a bounded sample")},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "params/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -237,6 +302,108 @@ def fill_grads(buf, n, seed, device):
         buf[lo:hi].copy_(g)
 
 
+def zero1_parity_check(dev, rank, world, zero1_kwargs):
+    """N > 1, before anything is timed: the sharded step against the CPU oracle (the checker, outside
+    every timed region).  (1) Three ZeRO-1 steps of the reference's unit-test LM with per-rank
+    gradients g / N accumulated into the arenas (N a power of two: the reduced sum is exact), the
+    third with an inf in the last rank's shard: decisions, norms, gathered master / moments and
+    the all-gathered twins against the oracle on the reduced gradients, and every arena left
+    zeroed.  (2) One slice of the 2,773,419,680-parameter arena per rank (ranks spread over it, the
+    upper ones above 2^31) through the split form with a handed-in sum of squares, against the
+    oracle on the same slice.  Returns the `parity` object of the JSON line; any mismatch makes
+    every rank exit non-zero."""
+    import math
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from anni_b200.capi import DT_BF16, DT_F32
+    from anni_b200.engine import LM_SHAPES, OptStep, lm_segments
+    from anni_b200.zero1 import Zero1
+    from oracle_lib import Oracle
+    from parity_util import bf16_bits_from_f32, check_step, f32_ulp_dist, make_inputs, to_dev, to_host
+
+    orc = Oracle()
+    problems = []
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    z = Zero1(segs, grad_dtype=DT_BF16, state_dtype=DT_F32, device=dev, **zero1_kwargs)
+    rng = np.random.default_rng(321)
+    p = rng.normal(0, 0.02, n).astype(np.float32)
+    m = rng.normal(0, 1e-4, n).astype(np.float32)
+    v = np.abs(rng.normal(0, 1e-6, n)).astype(np.float32)
+    p0 = p.copy()
+    z.load_shard_from_full(to_dev(p, dev), to_dev(m, dev), to_dev(v, dev))
+    skip_identical = True
+    for step in range(3):
+        base = rng.normal(0, 1e-3, n).astype(np.float32)
+        if step == 2:
+            base[n - 7] = np.inf
+        gb = torch.from_numpy(base).to(torch.bfloat16)
+        z.grad_full[:n] += (gb.float() / world).to(torch.bfloat16).to(dev)
+        z.step(OptStep.hyper(lr=3e-4, t=step + 1, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0))
+        st = z.status()
+        info = orc.step(p, orc.bf16_rne(base), m, v, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1,
+                        clip=1.0, grad_scale=1.0, t_before=step, check_finite=True,
+                        seg_off=segs.offsets, seg_flags=segs.flag_array)
+        if bool(st.skipped) != info["skipped"] or st.error != 0:
+            skip_identical = False
+            problems.append(f"step {step}: skipped {st.skipped} error {st.error}, oracle skipped {info['skipped']}")
+        if not info["skipped"] and not abs(st.norm - info["norm"]) <= 1e-9 * info["norm"]:
+            problems.append(f"step {step}: norm {st.norm} against {info['norm']}")
+        if bool(z.grad_full.any()):
+            problems.append(f"step {step}: gradient arena not left zeroed")
+    gp, gm, gv = (to_host(z.gather_full(x)) for x in (z.master, z.m, z.v))
+    max_ulp = int(f32_ulp_dist(gp, p).max())
+    try:
+        check_step(dict(p=gp, m=gm, v=gv), p, m, v, p0, exact_moments=False)
+    except AssertionError as e:
+        problems.append(f"sharded state against the oracle: {e}")
+    if not np.array_equal(to_host(z.twin_full[:n]), bf16_bits_from_f32(gp)):
+        problems.append("all-gathered twins are not the RNE cast of the master")
+    del z
+
+    segs4 = lm_segments(**LM_SHAPES["synth3b"], wd="matrices")
+    length = 1 << 20
+    off = (segs4.n - length) // max(1, world - 1) * rank // 4096 * 4096
+    so = segs4.offsets
+    first = int(np.searchsorted(so, off, side="right") - 1)
+    last = int(np.searchsorted(so, off + length, side="left"))
+    loc_off = np.clip(so[first:last + 1] - off, 0, length).astype(np.int64)
+    p4, g4, m4, v4 = make_inputs(length, seed=4000 + rank, grad_dtype=DT_BF16, state_dtype=DT_F32, grad_std=3e-4)
+    ss = orc.sumsq(g4, 1.0) * (segs4.n / length)
+    coef = 1.0 * (1.0 / (math.sqrt(ss) * 1.0 + 1e-12))
+    ref = [x.copy() for x in (p4, g4, m4, v4)]
+    orc.step(*ref, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=0.0, grad_scale=coef, t_before=41,
+             seg_off=loc_off, seg_flags=segs4.flag_array[first:last].copy())
+    eng = OptStep(segs4, grad_dtype=DT_BF16, state_dtype=DT_F32, shard_off=off, shard_n=length, device=dev).allocate()
+    for t, src in ((eng.master, p4), (eng.grad, g4), (eng.m, m4), (eng.v, v4)):
+        t[:length].copy_(to_dev(src, dev))
+    eng.reduce_tensor().copy_(torch.tensor([ss, 0.0], dtype=torch.float64))
+    eng.update(OptStep.hyper(lr=3e-4, t=42, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0))
+    st = eng.status()
+    out = dict(p=to_host(eng.master[:length]), m=to_host(eng.m[:length]), v=to_host(eng.v[:length]))
+    try:
+        assert st.error == 0 and st.skipped == 0 and st.eff_scale == coef
+        check_step(out, ref[0], ref[2], ref[3], p4, exact_moments=True)
+        assert np.array_equal(to_host(eng.twin_bf16[:length]), bf16_bits_from_f32(out["p"]))
+    except AssertionError as e:
+        problems.append(f"3B-arena slice at offset {off}: {e}")
+    max_ulp = max(max_ulp, int(f32_ulp_dist(out["p"], ref[0]).max()))
+    eng.close()
+
+    flag = torch.tensor([0 if problems else 1, max_ulp], dtype=torch.int64, device=dev)
+    mins = flag.clone()
+    dist.all_reduce(mins, op=dist.ReduceOp.MIN)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    ok = bool(mins[0].item())
+    if problems:
+        print(f"[bench] rank {rank}: parity check failed: " + "; ".join(problems), file=sys.stderr, flush=True)
+    return dict(checked=True, ok=ok, max_ulp_p=int(flag[1].item()), skip_identical=skip_identical and ok,
+                steps=3, arena_left_zeroed=ok, slices_of_3b_arena=world,
+                against="CPU oracle on the reduced gradients, before the timed region")
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -259,9 +426,15 @@ def run_ours(args):
     n = segs.n
     assert args.workload != WORKLOAD or n == N_PARAMS
     mode = os.environ.get("ANNI_B200_ZERO1_MODE", "")          # "", "peer", "copy" or "nccl"
-    z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev,
-              peer={"": None, "peer": True, "copy": "copy", "nccl": False}[mode],
-              multicast=os.environ.get("ANNI_B200_MULTICAST", "0") == "1")
+    zero1_kwargs = dict(peer={"": None, "peer": True, "copy": "copy", "nccl": False}[mode],
+                        multicast=os.environ.get("ANNI_B200_MULTICAST", "0") == "1")
+    parity = None
+    if world > 1:
+        parity = zero1_parity_check(dev, rank, world, zero1_kwargs)
+        if not parity["ok"]:
+            dist.destroy_process_group()
+            return 3
+    z = Zero1(segs, grad_dtype=gdt, state_dtype=sdt, device=dev, **zero1_kwargs)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     z.master.normal_(0, 0.02, generator=gen)
@@ -269,9 +442,9 @@ def run_ours(args):
     z.v.copy_(torch.randn(z.per, device=dev, generator=gen).mul_(1e-6).abs_())
 
     K, W = args.steps, args.warmup
-    # one rank: the step consumes (zeroes) its gradient arena, so every step gets a fresh one;
-    # several ranks: the arenas are only read (the reduced shard is what gets zeroed): four, cycled
-    pool_n = min(K + W, 48 if n < 1_000_000_000 else 8) if world == 1 else 4
+    # the step consumes (zeroes) the gradient arena it is given -- the whole local arena, on one
+    # rank as on several -- so every step gets a fresh one
+    pool_n = min(K + W, 48 if n < 1_000_000_000 else 8)
     pool = [z.new_grad_arena() for _ in range(pool_n)]
 
     def refill():
@@ -305,19 +478,14 @@ def run_ours(args):
         z.step(hyper(t))
         t += 1
         done += 1
-    if world > 1:
-        done = 0            # arenas are not consumed: no refills between batches
     total_ms, launches0 = 0.0, kernel_launches()
     phase_ms = {}
     step_ms = []
     left = K
     wall0 = time.time()
     while left > 0:
-        if world > 1:
-            batch = left
-        else:
-            batch = min(left, pool_n - (done % pool_n)) if done % pool_n else min(left, pool_n)
-        if world == 1 and done % pool_n == 0 and done > 0:
+        batch = min(left, pool_n - (done % pool_n)) if done % pool_n else min(left, pool_n)
+        if done % pool_n == 0 and done > 0:
             refill()
             torch.cuda.synchronize()
             time.sleep(1.0)
@@ -331,12 +499,19 @@ def run_ours(args):
             if world > 1:
                 evs = [torch.cuda.Event(enable_timing=True)]
                 evs[0].record()
-
-                def rec(name, evs=evs):
-                    e = torch.cuda.Event(enable_timing=True)
-                    e.record()
-                    evs.append((name, e))
-                z.step(hyper(t), record=rec, grads_complete=True)
+                if z.driver == "library":
+                    # the sequence runs inside the library, which records these events after each phase
+                    ph = [torch.cuda.Event(enable_timing=True) for _ in Zero1.PHASES]
+                    for e in ph:
+                        e.record()
+                    z.step(hyper(t), grads_complete=True, phase_events=ph)
+                    evs += list(zip(Zero1.PHASES, ph))
+                else:
+                    def rec(name, evs=evs):
+                        e = torch.cuda.Event(enable_timing=True)
+                        e.record()
+                        evs.append((name, e))
+                    z.step(hyper(t), record=rec, grads_complete=True)
                 marks.append(evs)
             else:
                 z.step(hyper(t))
@@ -420,6 +595,56 @@ def run_ours(args):
         split_ms = {"norm": sum(a.elapsed_time(b) for a, b, _ in marks) / k_sp,
                     "update": sum(b.elapsed_time(c) for _, b, c in marks) / k_sp}
 
+    # ---- several ranks: this rank's share of the update on its own memory alone ------------------
+    # (what falls linearly with N; the step as a whole is bound by the two collectives on the wire)
+    hbm_only_ms = None
+    if world > 1 and hasattr(z.eng, "update_range") and z.shard_n > 0:
+        evs = []
+        barrier()
+        for i in range(2 + 5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            z.eng.update_range(hyper(t), 0, z.shard_n, first=True, last=True, local_twins=True)
+            b.record()
+            t += 1
+            evs.append((a, b))
+        barrier()
+        hbm_only_ms = sum(a.elapsed_time(b) for a, b in evs[2:]) / 5
+        tmax = torch.tensor([hbm_only_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        hbm_only_ms = float(tmax.item())
+
+    # ---- sustained: 200 steps back to back, no pauses (one rank) ---------------------------------
+    # Each step is preceded by an untimed device copy that restores the gradient arena the previous
+    # step consumed, so the GPU never idles; the step itself is timed by its own pair of events.
+    sustained = None
+    if world == 1:
+        n_sus = 200
+        gsrc = torch.empty(z.padded, dtype=z.grad_full.dtype, device=dev)
+        fill_grads(gsrc, n, 4242, dev)
+        bind_grads(pool[0])
+        arena = pool[0][0]
+        evs = []
+        torch.cuda.synchronize()
+        sus0 = time.time()
+        for i in range(n_sus + 10):
+            arena.copy_(gsrc)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            z.step(hyper(t))
+            b.record()
+            t += 1
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        sus1 = time.time()
+        ts = sorted(a.elapsed_time(b) for a, b in evs[10:])
+        sus_ms = sum(ts) / len(ts)
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms, "p50_ms": ts[len(ts) // 2], "value": n / (sus_ms * 1e-3),
+                     "roofline_frac": alg_bytes * n / (sus_ms * 1e-3) / 1e9 / measured_peaks()[0],
+                     "window_s": sus1 - sus0,
+                     "note": "back-to-back steps, each after an untimed device copy that restores the gradient arena"}
+        del gsrc
+
     # ---- e2e: host gradient buffers through the C ABI --------------------------------------
     e2e_steps = max(2, min(5, K))
     host = [torch.empty(z.padded, dtype=z.grad_full.dtype).pin_memory() for _ in range(2)]
@@ -445,10 +670,50 @@ def run_ours(args):
         e2e_sec = float(tmax.item())
     e2e_value = n * e2e_steps / e2e_sec
 
+    # ---- e2e through the C optimizer object: host fp32 gradients of configuration 1 -------------
+    # anni_lm_adam_step_scaled as a C trainer calls it: uploads the host gradient arrays (pinned),
+    # runs the one-launch step, reads the status back, zeroes the host gradients.
+    e2e_c = None
+    if world == 1 and args.workload == WORKLOAD:
+        from anni_b200 import lm_adam
+        del pool, host
+        torch.cuda.empty_cache()
+        segs1 = lm_segments(**LM_SHAPES["talk170m"], wd="matrices")
+        n1 = segs1.n
+        hw = torch.empty(n1, dtype=torch.float32).pin_memory()
+        hg = torch.empty(n1, dtype=torch.float32).pin_memory()
+        src = torch.empty(n1, dtype=torch.float32, device=dev)
+        fill_grads(src, n1, 99, dev)
+        gsrc1 = src.cpu()
+        hw.normal_(0, 0.02)
+        del src
+        L1 = lm_adam.lib()
+        opt = lm_adam.create(segs1, hw.data_ptr(), hg.data_ptr())
+        o = opt.contents
+        o.beta2, o.weight_decay, o.grad_clip = HYPER["beta2"], HYPER["wd"], HYPER["clip"]
+        secs = []
+        for i in range(2 + 4):
+            hg.copy_(gsrc1)                       # the backward pass's output, untimed
+            t0 = time.perf_counter()
+            rc = L1.anni_lm_adam_step_scaled(opt, HYPER["lr"], 1.0)
+            secs.append(time.perf_counter() - t0)
+            assert rc == 0 and o.last_skipped == 0
+        L1.anni_lm_adam_free(ctypes.byref(opt))
+        sec = sum(secs[2:]) / len(secs[2:])
+        e2e_c = {"value": n1 / sec, "unit": "params/s", "workload": "talk170m-fp32 (configuration 1)",
+                 "n_params": n1, "ms_per_step": sec * 1e3, "h2d_bytes_per_step": 4 * n1,
+                 "d2h_bytes_per_step": 48, "steps": len(secs) - 2,
+                 "path": "anni_lm_adam_step_scaled: upload of pinned host fp32 gradients (147 tensors), "
+                         "one-launch step, status read, host gradients zeroed"}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return 0
+    if sustained is not None and sampler:
+        sc = sampler.window(sus0, sus1)
+        sustained["sm_mhz"] = sc["sm_mhz"]
+        sustained["reasons"] = sc["reasons"]
     clocks = sampler.finish(wall0, wall1) if sampler else None
     peak, peak_kind = measured_peaks()
     # the dominant kernel's share of the step: at N = 1 the step IS one launch of it
@@ -484,12 +749,25 @@ def run_ours(args):
         "clocks": clocks,
         "status": {"norm": st.norm, "skipped": int(st.skipped), "error": int(st.error)},
     }
+    if parity is not None:
+        line["parity"] = parity
+    if e2e_c is not None:
+        line["e2e_c_api"] = e2e_c
+    if sustained is not None:
+        line["sustained"] = sustained
     if world > 1:
         line["phases_ms"] = {k: v / K for k, v in phase_ms.items()}
+        if hbm_only_ms is not None:
+            line["phases_ms"]["update_hbm_only"] = hbm_only_ms
+            line["per_rank_update"] = {
+                "ms": hbm_only_ms, "shard_params": shard_n,
+                "roofline_frac": alg_bytes * shard_n / (hbm_only_ms * 1e-3) / 1e9 / peak,
+                "note": "this rank's update on local memory alone (twins stored locally, the full local "
+                        "gradient arena cleared): the part of the step that shrinks with N"}
         wire = (world - 1) / world * n * 2 / 1e9            # GB each way per GPU, per collective
         rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
         ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
-        line["nvlink"] = {"mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
+        line["nvlink"] = {"driver": z.driver, "mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
                                    else "copy engines + local kernels" if getattr(z, "copy_mode", False)
                                    else "peer kernels" if z.peer else "nccl"), "wire_gb_per_collective": wire,
                           "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,

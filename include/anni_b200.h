@@ -142,8 +142,9 @@ int	anni_optstep_bind(anni_optstep *h, const anni_optstep_buffers *buf);
 /*
 ** Whole step in ONE cooperative launch on `stream` (a cudaStream_t, NULL = the
 ** legacy stream): norm phase, device-wide bounded barrier, decision, update
-** phase, twin emission, and for fp8 segments a second barrier and the
-** quantising phase.  Replaces the reference sequence gpu_grad_sumsq -> host
+** phase, twin emission; for fp8 segments the quantiser follows the update tensor
+** by tensor inside the same phase (each tensor's codes are written as soon as the
+** whole grid has left it, while its fresh master is still in L2).  Replaces the reference sequence gpu_grad_sumsq -> host
 ** sqrt/clip/skip -> gpu_adam_step_dev_bf16 (lang/lm_adam.c:466-493) and its two
 ** host round trips.  Single-GPU form: the norm is this shard's alone.
 */
@@ -161,6 +162,15 @@ int	anni_optstep_step(anni_optstep *h, const anni_optstep_hyper *hp, void *strea
 int	anni_optstep_norm(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
 int	anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp, void *stream);
 int	anni_optstep_quantize(anni_optstep *h, void *stream);
+/*
+** The step for a caller whose gradient PRODUCER already knows the sum of squares (the last
+** epilogue of the backward pass, a reduce-scatter that squares what it writes): no norm pass, so
+** the gradients are read once.  d_sumsq: device double[2] = {sum of squares of the raw gradients,
+** count of non-finite values (0 if none)}, read when the stream gets there.  Otherwise identical
+** to anni_optstep_step, e4m3 twins included (two launches then, the update and the quantiser).
+*/
+int	anni_optstep_step_with_sumsq(anni_optstep *h, const anni_optstep_hyper *hp, const double *d_sumsq,
+		void *stream);
 double	*anni_optstep_reduce_buffer(anni_optstep *h);	/* device double[2] */
 float	*anni_optstep_amax_buffer(anni_optstep *h);	/* device float[n_seg] */
 float	*anni_optstep_scale_buffer(anni_optstep *h);	/* device float[n_seg]: dequantisation scales */
@@ -271,6 +281,28 @@ int	anni_arena_free(void *ptr, size_t mapped_bytes);
 int	anni_optstep_set_multicast(anni_optstep *h, const void *mc_grad, void *mc_twin,
 		void *mc_twin_fp8, uint64_t arena_off_padded);
 
+/*
+** Order in which the peers set by anni_optstep_set_peers are visited: `first` (an index into those
+** arrays) comes first, the others follow cyclically.  Give every rank a different start --
+** (rank + 1) % n_peers puts the remote copies first and the rank's own last -- so that at any
+** moment the ranks pull from, and store to, different peers instead of all starting at rank 0.
+** The reduce kernel adds the copies in that order (float addition: the result is the same on
+** every run, but differs in the last bit from another order unless the sum is exact).
+*/
+int	anni_optstep_rotate_peers(anni_optstep *h, int first);
+/*
+** ZeRO-1 and "the step leaves the gradients zeroed" (lang/lm_adam.c:597, num/gpu.h:125-127 of the
+** reference; its trainer relies on it, lang/lm_train.c:1220-1226): the buffer the backward pass
+** accumulates into is this rank's FULL gradient arena, not the reduced shard the update works on.
+** Name that arena here (`arena` = its element 0, `parts` shards of `stride` elements each, stride
+** a multiple of 8 and >= this engine's shard) and anni_optstep_update / _update_range with
+** ANNI_STEP_ZERO_GRAD clear the whole arena -- element e of every part where they would have
+** cleared the bound gradient buffer, plus the ends of the parts beyond this shard's length --
+** instead of that buffer.  Queue the update after every peer has read the arena (the all-reduce
+** of the reduce buffer says so).  arena = NULL: back to clearing the bound buffer.
+*/
+int	anni_optstep_set_grad_arena(anni_optstep *h, void *arena, uint64_t stride, int parts);
+
 /* Blocks until `stream` has finished the queued steps, then copies the status. */
 int	anni_optstep_status_read(anni_optstep *h, anni_optstep_status *out, void *stream);
 
@@ -297,7 +329,9 @@ int	anni_optstep_loss_scale_init(anni_optstep *h, double scale, int growth_inter
 **     a single stream; calls that overlap on the GPU corrupt each other;
 **   - the first call on a device resolves the array's device address: make it
 **     during start-up, before any stream capture on that device;
-**   - ANNI_STEP_DEV_LOSS_SCALE is not available (fold 1/loss_scale into grad_scale).
+**   - ANNI_STEP_DEV_LOSS_SCALE is not available (fold 1/loss_scale into grad_scale);
+**   - cfg->seg_off / seg_flags are copied from host memory by every call: keep them valid until
+**     the call returns; a stream in capture mode is refused with ANNI_E_ARG.
 ** cfg, buf, hp as for create / bind / step.  seg_scale_out (device, n_seg floats,
 ** may be NULL) receives the e4m3 dequantisation scales when fp8 twins are asked for.
 */

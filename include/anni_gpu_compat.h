@@ -53,8 +53,9 @@ void	gpu_set_fp8(int on);					/* gpu.h:30 */
 void	gpu_set_fp8_dgrad(int on);				/* gpu.h:31 */
 int	gpu_fp8(void);						/* gpu.h:32 */
 void	gpu_device_sync(void);					/* gpu.h:38 */
-/* Blocks of 8 MB and more are compressible device memory where the GPU offers it (anni_arena_alloc
-** in anni_b200.h): same contents and behaviour, but release them with gpu_free, never cudaFree. */
+/* Plain cudaMalloc memory.  With ANNI_B200_COMPRESSIBLE_MALLOC=1 blocks of 8 MB and more are compressible
+** device memory where the GPU offers it (anni_arena_alloc in anni_b200.h; zeroed, this device only):
+** release every block with gpu_free, never cudaFree. */
 void	*gpu_malloc(size_t nbytes);				/* gpu.h:40 */
 void	gpu_free(void *p);					/* gpu.h:41 */
 int	gpu_memcpy_h2d(void *dst, const void *src, size_t nbytes);	/* gpu.h:42 */
@@ -75,6 +76,10 @@ int	gpu_grad_sumsq(const ann_real_t *d_x, int n, double *out);	/* gpu.h:123 */
 int	gpu_adam_step_dev_bf16(ann_real_t *d_param, void *d_param_bf16, ann_real_t *d_grad,
 		ann_real_t *d_m, ann_real_t *d_v, int n, double lr, double beta1, double beta2,
 		double eps, int t, double grad_scale);		/* gpu.h:129-132 */
+/* db_host[cols] += column sums of the rows x cols device matrix x.  Done on the device, straight into the
+** optimizer's gradient flat, when db_host is the host vector of a tensor attached with
+** anni_lm_adam_alias_vec (anni_lm_adam.h); -1 otherwise (the caller's CPU path). */
+int	gpu_mat_col_sum_add(ann_real_t *db_host, const ann_real_t *x, int rows, int cols);	/* gpu.h:198 */
 int	gpu_mat_axpy(anni_mat *y, double a, const anni_mat *x);	/* gpu.h:299 */
 unsigned	gpu_param_epoch(void);				/* gpu.h:346 */
 
@@ -84,6 +89,13 @@ unsigned	gpu_param_epoch(void);				/* gpu.h:346 */
 ** the pointer is outside the registered flat or no flat is registered.
 */
 void	*anni_half_wt_lookup(const ann_real_t *fp32_dev, size_t n);
+/*
+** ANN_OP_PROF (gpu.h:66, num/gpu_cuda.cu:3205-3409): anni_op_prof_enable overrides the environment
+** variable; anni_op_prof_totals waits for the device and returns the accumulated milliseconds and
+** calls of one row of the table ("adam", "sumsq", "colsum", "axpy", "convert") without resetting it.
+*/
+void	anni_op_prof_enable(int on);
+int	anni_op_prof_totals(const char *name, double *ms, long *calls);
 /* 64-bit forms of the two legacy calls (the reference's `int n` stops at 2^31-1). */
 int	anni_grad_sumsq64(const void *d_x, int dtype, unsigned long long n, double *out);
 int	anni_adam_step_dev64(ann_real_t *d_param, void *d_param_bf16, ann_real_t *d_grad,

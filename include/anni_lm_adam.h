@@ -123,6 +123,18 @@ int	anni_lm_adam_upload_grads(anni_lm_adam *opt);
 int	anni_lm_adam_prepare(anni_lm_adam *opt);
 int	anni_lm_adam_alias(anni_lm_adam *opt, int tensor, anni_mat *w, anni_mat *dw);
 /*
+** The same for a bias or LayerNorm VECTOR, which the reference keeps on the host and moves twice
+** per step (seg_gather / seg_scatter, lang/lm_adam.c:361-429: the "~1.8 ms of small copies" its
+** own audit names): after this call the tensor's gradient lives in the device flat only.  What the
+** host vector holds at that moment is uploaded once, the step stops uploading it, and (fp32
+** gradients) the host vector's address is remembered so that gpu_mat_col_sum_add -- the call the
+** backward pass makes with that address, num/gpu.h:198 -- adds its column sums straight into the
+** flat (the reference's per-vector device accumulators, colsum_flush_all, num/gpu_cuda.cu:3142,
+** without the flush).  d_w / d_dw (may be NULL) receive the device addresses of the tensor's
+** weights and gradients for producers that write them directly.  Call after anni_lm_adam_prepare.
+*/
+int	anni_lm_adam_alias_vec(anni_lm_adam *opt, int tensor, float **d_w, void **d_dw);
+/*
 ** Snapshot of m and v for a checkpoint without stalling the step stream (the reference's offload
 ** copies synchronously, lang/lm_adam.c:314-334): begin queues device-to-host copies into pinned
 ** staging on a side stream that first waits for the work queued so far; finish waits for them

@@ -9,7 +9,10 @@
 ** gpu_malloc'd flats, aliasing, gpu_grad_sumsq, host clip/skip,
 ** gpu_adam_step_dev_bf16, pinned scatter of the host-resident vectors -- all
 ** through this library's symbols.  Built by oracle/Makefile into
-** oracle/_ref/libannref_dropin.so.
+** oracle/_ref/libannref_dropin.so, and a second time (-DDROPIN_FUSED) with
+** lm_adam_fused_step.patch applied to a copy of lang/lm_adam.c into
+** oracle/_ref/libannref_fused.so: the same trainer-side code with the one-launch
+** engine behind lm_adam_step_scaled (used_gpu then returns 1 + the steps it took).
 */
 #include <stdio.h>
 #include <stdlib.h>
@@ -132,6 +135,17 @@ int dropin_run(int n_t, const int *kinds, const int *rows, const int *cols, floa
 			rc = rc ? rc : -13;
 		}
 	}
+#ifdef DROPIN_FUSED
+	/* built with lm_adam_fused_step.patch: every step must have gone through the one-launch engine */
+	{
+		extern int lm_adam_b200_steps;
+
+		if (*used_gpu && lm_adam_b200_steps < steps && rc == 0)
+			rc = -14;
+		*used_gpu = *used_gpu ? 1 + lm_adam_b200_steps : 0;
+		lm_adam_b200_steps = 0;
+	}
+#endif
 	lm_adam_free(&opt);
 	for (i = 0; i < n_t; i++) {
 		if (w[i])

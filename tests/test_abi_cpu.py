@@ -28,7 +28,7 @@ def _declared_symbols(header):
     return names
 
 
-@pytest.mark.parametrize("header", ["anni_b200.h", "anni_gpu_compat.h", "anni_lm_adam.h"])
+@pytest.mark.parametrize("header", ["anni_b200.h", "anni_gpu_compat.h", "anni_lm_adam.h", "anni_zero1.h"])
 def test_every_declared_symbol_is_exported(header):
     L = capi.lib()
     names = _declared_symbols(header)
@@ -139,3 +139,55 @@ def test_part_wise_calls_and_helpers_refuse_bad_arguments():
     if not torch.cuda.is_available():                       # without a device the allocator says so
         assert L.anni_arena_alloc(1 << 20, C.byref(p), C.byref(size), C.byref(comp)) in (capi.E_CUDA, capi.E_LIMIT)
         assert not p.value and size.value == 0
+
+
+def test_zero1_driver_geometry_and_argument_checks():
+    """anni_zero1_*: the shard geometry equals the Python driver's, and create judges its
+    arguments before it touches a device or the communicator -- checked here with made-up
+    arena addresses and a made-up communicator handle, none of which is ever dereferenced."""
+    from anni_b200.capi import DT_BF16, DT_F32, E_ARG, OK, Zero1Config
+    from anni_b200.zero1 import shard_geometry
+    L = capi.lib()
+    u64 = C.c_uint64
+    for n, world in ((138156, 2), (555_762_080, 8), (2_773_419_680, 8), (5000, 8), (100, 1)):
+        per, own = shard_geometry(n, world)
+        for rank in range(world):
+            a, b, c = u64(), u64(), u64()
+            assert L.anni_zero1_geometry(n, world, rank, C.byref(a), C.byref(b), C.byref(c)) == OK
+            assert a.value == per and c.value == own[rank][1]
+            assert b.value == min(own[rank][0], n)
+    assert L.anni_zero1_geometry(100, 9, 0, None, None, None) == E_ARG         # more ranks than one NVSwitch domain
+    assert L.anni_zero1_geometry(100, 2, 2, None, None, None) == E_ARG
+
+    off = np.array([0, 600, 1000], np.int64)
+    flg = np.array([3, 2], np.uint32)
+    fake = 0x7f0000001000                                                      # never dereferenced
+
+    def cfg(**kw):
+        c = Zero1Config()
+        c.n_arena, c.grad_dtype, c.state_dtype = 1000, DT_BF16, DT_F32
+        c.n_seg, c.seg_off, c.seg_flags = 2, off.ctypes.data, flg.ctypes.data
+        c.rank, c.world, c.nccl_comm = 0, 2, fake
+        c.grad_arena, c.twin_arena = fake + 0x1000, fake + 0x2000
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return c
+    h = C.c_void_p()
+    for bad in (dict(world=0), dict(world=9), dict(rank=2), dict(rank=-1), dict(grad_dtype=7),
+                dict(nccl_comm=None), dict(grad_arena=None), dict(twin_arena=None), dict(n_seg=-1),
+                dict(seg_off=None)):
+        assert L.anni_zero1_create(C.byref(cfg(**bad)), C.byref(h)) == E_ARG, bad
+        assert not h.value
+    # e4m3 twins asked for, but no arena for them
+    flg8 = np.array([5, 2], np.uint32)
+    assert L.anni_zero1_create(C.byref(cfg(seg_flags=flg8.ctypes.data)), C.byref(h)) == E_ARG
+    # peer mode: this rank's entry must be its own arena
+    arr = (C.c_void_p * 2)(fake + 0x9000, fake + 0xa000)
+    tw = (C.c_void_p * 2)(fake + 0x2000, fake + 0xb000)
+    assert L.anni_zero1_create(C.byref(cfg(peer_grad=C.cast(arr, C.c_void_p), peer_twin=C.cast(tw, C.c_void_p))),
+                               C.byref(h)) == E_ARG
+    assert L.anni_zero1_create(None, C.byref(h)) == E_ARG and L.anni_zero1_create(C.byref(cfg()), None) == E_ARG
+    assert L.anni_zero1_step(None, None, 0, None, None) == E_ARG
+    assert L.anni_zero1_unique_id(None) == E_ARG
+    assert L.anni_zero1_comm_init(None, 0, 2, C.byref(h)) == E_ARG
+    assert L.anni_zero1_nccl_available() in (0, 1)

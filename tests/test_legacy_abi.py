@@ -16,6 +16,7 @@ from parity_util import bf16_bits_from_f32, check_step, f32_ulp_dist, make_input
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DROPIN = os.path.join(ROOT, "oracle", "_ref", "libannref_dropin.so")
+FUSED = os.path.join(ROOT, "oracle", "_ref", "libannref_fused.so")
 HYP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
 d = C.c_double
 
@@ -179,12 +180,20 @@ def test_gradient_buffer_helpers():
 
 @pytest.mark.skipif(not os.path.exists(DROPIN), reason="oracle/_ref/libannref_dropin.so not built")
 @pytest.mark.parametrize("bf16_prec", [0, 1])
-def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec):
-    """The reference's own lang/lm_adam.c (unmodified, with its num/mat.c, num/vec.c) linked
-    against libanni_b200.so in place of its backend: three steps take its device path and land
-    on the oracle's numbers."""
+@pytest.mark.parametrize("build", ["unmodified", "fused"])
+def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec, build):
+    """The reference's own lang/lm_adam.c (with its num/mat.c, num/vec.c) linked against
+    libanni_b200.so in place of its backend: three steps take its device path and land on the
+    oracle's numbers.  "unmodified": the file as it is -- the two-call sequence gpu_grad_sumsq /
+    gpu_adam_step_dev_bf16 with the host deciding in between.  "fused": the same file with
+    oracle/lm_adam_fused_step.patch applied (the change a maintainer makes to put the one-launch
+    engine behind lm_adam_step_scaled); the driver then also checks that every step went through
+    the engine."""
     capi.lib()
-    R = C.CDLL(DROPIN)
+    lib = DROPIN if build == "unmodified" else FUSED
+    if not os.path.exists(lib):
+        pytest.skip(f"{os.path.basename(lib)} not built")
+    R = C.CDLL(lib)
     R.dropin_run.restype = C.c_int
     segs = lm_segments(**LM_SHAPES["tiny"], wd="all")
     kinds = np.array([0 if (f & 1) and s > 300 else 1 for f, s in zip(lm_segments(**LM_SHAPES["tiny"]).flags,
@@ -205,7 +214,7 @@ def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec):
     rc = R.dropin_run(len(kinds), ptr(kinds), ptr(rows), ptr(cols), ptr(pp), ptr(g), ptr(m), ptr(v),
                       steps, d(1e-3), d(0.9), d(0.95), d(1e-8), d(0.1), d(1.0), d(0.25),
                       bf16_prec, ptr(norms), C.byref(used))
-    assert rc == 0 and used.value == 1
+    assert rc == 0 and used.value == (1 if build == "unmodified" else 1 + steps)
     rp, rm, rv = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
     for s in range(steps):
         gg = g[s].copy()
@@ -223,45 +232,12 @@ def test_reference_optimizer_runs_on_this_library(oracle, bf16_prec):
 
 # ---- the library's own optimizer object (C mirror of lm_adam) -------------------------------
 
-class Tensor(C.Structure):
-    _fields_ = [("w", C.c_void_p), ("dw", C.c_void_p), ("n", C.c_int64), ("flags", C.c_uint32)]
-
-
-class Seg(C.Structure):
-    _fields_ = [("w", C.c_void_p), ("dw", C.c_void_p), ("off", C.c_int64), ("n", C.c_int64),
-                ("flags", C.c_uint32), ("w_mat", C.c_void_p), ("dw_mat", C.c_void_p)]
-
-
-class LmAdam(C.Structure):
-    _fields_ = [("segs", C.POINTER(Seg)), ("n_segs", C.c_int), ("n", C.c_int64), ("t", C.c_int),
-                ("beta1", d), ("beta2", d), ("eps", d), ("h_m", C.POINTER(C.c_float)),
-                ("h_v", C.POINTER(C.c_float)), ("d_param", C.c_void_p), ("d_param_bf16", C.c_void_p),
-                ("d_param_fp8", C.c_void_p), ("d_grad", C.c_void_p), ("d_m", C.c_void_p),
-                ("d_v", C.c_void_p), ("dev_mv", C.c_int), ("params_valid", C.c_int),
-                ("offload_mv", C.c_int), ("weight_decay", d), ("grad_clip", d), ("last_grad_norm", d),
-                ("grad_dtype", C.c_int), ("state_dtype", C.c_int), ("last_skipped", C.c_int),
-                ("last_error", C.c_int), ("loss_scale", d), ("exact_update", C.c_int),
-                ("snap_m", C.c_void_p), ("snap_v", C.c_void_p), ("snap_stream", C.c_void_p),
-                ("snap_event", C.c_void_p), ("grad_arena_bytes", C.c_size_t), ("engine", C.c_void_p)]
+from anni_b200.lm_adam import LmAdam, Mat, Seg, Tensor  # noqa: E402
+from anni_b200 import lm_adam as lm_adam_mod  # noqa: E402
 
 
 def _mirror():
-    L = capi.lib()
-    L.anni_lm_adam_create.restype = C.POINTER(LmAdam)
-    L.anni_lm_adam_create.argtypes = [C.POINTER(Tensor), C.c_int, C.c_int, C.c_int]
-    L.anni_lm_adam_free.argtypes = [C.POINTER(C.POINTER(LmAdam))]
-    L.anni_lm_adam_step_scaled.restype = C.c_int
-    L.anni_lm_adam_step_scaled.argtypes = [C.POINTER(LmAdam), d, d]
-    L.anni_lm_adam_step.restype = C.c_int
-    L.anni_lm_adam_step.argtypes = [C.POINTER(LmAdam), d]
-    L.anni_lm_adam_sync_host.restype = C.c_int
-    L.anni_lm_adam_sync_host.argtypes = [C.POINTER(LmAdam)]
-    L.anni_lm_adam_invalidate.argtypes = [C.POINTER(LmAdam)]
-    L.anni_lm_adam_zero_grad.argtypes = [C.POINTER(LmAdam)]
-    L.anni_lm_adam_set_offload.argtypes = [C.c_int]
-    L.anni_lm_adam_set_moments.restype = C.c_int
-    L.anni_lm_adam_set_moments.argtypes = [C.POINTER(LmAdam), C.c_void_p, C.c_void_p]
-    return L
+    return lm_adam_mod.lib()
 
 
 def _make_opt(L, segs, p, g):
@@ -499,3 +475,106 @@ def test_aliased_matrices_and_async_moment_snapshot(oracle):
         assert not w.d_data and not dw.d_data and w.on_device == 0 and dw.on_device == 0
     dp = np.abs(p.astype(np.float64) - rp)
     assert (dp <= 2 * np.spacing(np.abs(rp)) + 4e-9).all()
+
+
+def test_vector_gradients_stay_on_the_device(oracle, capfd, monkeypatch):
+    """Every tensor's gradient lives in the device flat: matrices as aliased views, bias / LayerNorm
+    vectors attached with anni_lm_adam_alias_vec, their gradients produced by gpu_mat_col_sum_add
+    (called with the HOST vector's address, as the backward pass does) straight into the flat.  The
+    step then uploads nothing; its result equals the oracle's on the gradients the device held.
+    Also here: the per-operation profile table (ANN_OP_PROF) and the periodic norm report."""
+    class Mat(C.Structure):
+        _fields_ = [("data", C.c_void_p), ("d_data", C.c_void_p), ("rows", C.c_int),
+                    ("cols", C.c_int), ("on_device", C.c_int)]
+    L = _mirror()
+    Lg = _legacy()
+    L.anni_lm_adam_prepare.restype = C.c_int
+    L.anni_lm_adam_prepare.argtypes = [C.POINTER(LmAdam)]
+    L.anni_lm_adam_alias.restype = C.c_int
+    L.anni_lm_adam_alias.argtypes = [C.POINTER(LmAdam), C.c_int, C.POINTER(Mat), C.POINTER(Mat)]
+    L.anni_lm_adam_alias_vec.restype = C.c_int
+    L.anni_lm_adam_alias_vec.argtypes = [C.POINTER(LmAdam), C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+    Lg.gpu_mat_col_sum_add.restype = C.c_int
+    Lg.gpu_mat_col_sum_add.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+    Lg.gpu_memcpy_h2d.restype = C.c_int
+    Lg.gpu_memcpy_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    Lg.anni_op_prof_enable.argtypes = [C.c_int]
+    Lg.anni_op_prof_totals.restype = C.c_int
+    Lg.anni_op_prof_totals.argtypes = [C.c_char_p, C.POINTER(C.c_double), C.POINTER(C.c_long)]
+    Lg.anni_op_prof_enable(1)
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n, off = segs.n, segs.offsets
+    p, g0, _, _ = make_inputs(n, seed=73)
+    g = np.zeros(n, np.float32)
+    g[off[1]:off[2]] = 0.25                     # what the host vector of b_head holds when it is attached
+    opt = _make_opt(L, segs, p, g)
+    o = opt.contents
+    o.beta2, o.weight_decay, o.grad_clip = 0.95, 0.1, 1.0
+    assert L.anni_lm_adam_alias_vec(opt, 1, None, None) == capi.E_ARG      # before the flats exist
+    assert L.anni_lm_adam_prepare(opt) == 0
+    views, vec_ptrs = {}, {}
+    for i in range(len(segs)):
+        if segs.flags[i] & 1:
+            rows = 64
+            w = Mat(p[off[i]:].ctypes.data, None, rows, segs.sizes[i] // rows, 0)
+            dw = Mat(g[off[i]:].ctypes.data, None, rows, segs.sizes[i] // rows, 0)
+            assert L.anni_lm_adam_alias(opt, i, C.byref(w), C.byref(dw)) == 0
+            views[i] = (w, dw)
+        else:
+            dwp, ddw = C.c_void_p(), C.c_void_p()
+            assert L.anni_lm_adam_alias_vec(opt, i, C.byref(dwp), C.byref(ddw)) == 0
+            assert dwp.value == o.d_param + 4 * off[i] and ddw.value == o.d_grad + 4 * off[i]
+            vec_ptrs[i] = ddw.value
+    for i in range(o.n_segs):
+        assert not o.segs[i].dw                                   # nothing left to upload
+    rows = 48
+    rng = np.random.default_rng(74)
+    for i in range(len(segs)):
+        sl = slice(int(off[i]), int(off[i + 1]))
+        if i in views:
+            chunk = np.ascontiguousarray(g0[sl])
+            assert Lg.gpu_memcpy_h2d(views[i][1].d_data, chunk.ctypes.data, chunk.nbytes) == 0
+        else:
+            cols = segs.sizes[i]
+            x = to_dev((rng.normal(0, 1e-3, (rows, cols)) / rows).astype(np.float32))
+            assert Lg.gpu_mat_col_sum_add(g[off[i]:].ctypes.data, x.data_ptr(), rows, cols) == 0
+            assert Lg.gpu_mat_col_sum_add(g[off[i]:].ctypes.data, x.data_ptr(), rows, cols) == 0   # accumulates
+    # a vector nobody attached, and a matrix that is not on the device: the caller's CPU path
+    other = np.zeros(64, np.float32)
+    x = torch.zeros(4, 64, device="cuda")
+    assert Lg.gpu_mat_col_sum_add(other.ctypes.data, x.data_ptr(), 4, 64) == -1
+    hostx = np.zeros((4, segs.sizes[1]), np.float32)
+    assert Lg.gpu_mat_col_sum_add(g[off[1]:].ctypes.data, hostx.ctypes.data, 4, segs.sizes[1]) == -1
+    Lg.gpu_device_sync()
+    flat = torch.empty(n, dtype=torch.float32, device="cuda")
+    Lg.gpu_memcpy_d2h.restype = C.c_int
+    Lg.gpu_memcpy_d2h.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    held = np.empty(n, np.float32)
+    assert Lg.gpu_memcpy_d2h(held.ctypes.data, o.d_grad, 4 * n) == 0
+    # column sums landed where the vectors live, on top of what the host vector held when attached
+    sl = slice(int(off[1]), int(off[2]))
+    assert np.all(np.abs(held[sl] - 0.25) < 0.01) and held[sl].std() > 0
+    for i in views:
+        assert np.array_equal(held[off[i]:off[i + 1]], g0[off[i]:off[i + 1]])
+    monkeypatch.setenv("ANN_GNORM_EVERY", "1")
+    assert L.anni_lm_adam_step_scaled(opt, 1e-3, 1.0) == 0
+    rp, rm, rv, rg = p.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32), held.copy()
+    info = oracle.step(rp, rg, rm, rv, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0, t_before=0,
+                       check_finite=True, seg_off=off, seg_flags=segs.flag_array)
+    assert abs(o.last_grad_norm - info["norm"]) <= 1e-9 * info["norm"]
+    assert Lg.gpu_memcpy_d2h(held.ctypes.data, o.d_grad, 4 * n) == 0 and not held.any()   # left zeroed
+    ms, calls = C.c_double(), C.c_long()
+    assert Lg.anni_op_prof_totals(b"adam", C.byref(ms), C.byref(calls)) == 0
+    assert calls.value >= 1 and ms.value > 0.0
+    assert Lg.anni_op_prof_totals(b"colsum", C.byref(ms), C.byref(calls)) == 0 and calls.value == 2 * len(vec_ptrs)
+    Lg.gpu_op_prof_dump()
+    err = capfd.readouterr().err
+    assert "[opprof]" in err and "adam" in err and "colsum" in err
+    assert Lg.anni_op_prof_totals(b"adam", C.byref(ms), C.byref(calls)) == 0 and calls.value == 0   # the dump resets
+    Lg.anni_op_prof_enable(0)
+    L.anni_lm_adam_free(C.byref(opt))
+    dp = np.abs(p.astype(np.float64) - rp)
+    assert (dp <= 2 * np.spacing(np.maximum(np.abs(rp), 1e-3)) + 2e-9).all()
+    # the registry forgot the freed flat: the same host vector is unknown again
+    x = torch.zeros(4, segs.sizes[1], device="cuda")
+    assert Lg.gpu_mat_col_sum_add(g[off[1]:].ctypes.data, x.data_ptr(), 4, segs.sizes[1]) == -1

@@ -103,3 +103,75 @@ def test_other_super_chunk_sizes_give_the_same_bits(sc, monkeypatch):
         assert torch.equal(ref.scale_tensor(), eng.scale_tensor())
         eng.close()
     ref.close()
+
+
+def test_update_clears_the_named_gradient_arena():
+    """ZeRO-1 on one GPU's worth of memory: an engine that owns the SECOND, shorter half of the arena
+    is told where the rank's full gradient arena lies (two parts); its update must leave that whole
+    arena zeroed -- both parts, and the ends of the parts beyond this shard's length -- while the
+    step's results are those of an engine that clears its bound buffer."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    stride = -(-(-(-n // 2)) // 4096) * 4096
+    off, cnt = stride, n - stride
+    assert 0 < cnt < stride
+    p, g, m, v = make_inputs(n, seed=8, grad_dtype=DT_BF16, state_dtype=DT_F32)
+    outs = []
+    for named in (False, True):
+        eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_F32, shard_off=off, shard_n=cnt).allocate()
+        eng.master[:cnt].copy_(to_dev(p[off:]))
+        eng.grad[:cnt].copy_(to_dev(g[off:]))
+        eng.m[:cnt].copy_(to_dev(m[off:]))
+        eng.v[:cnt].copy_(to_dev(v[off:]))
+        arena = torch.ones(2 * stride, dtype=torch.bfloat16, device="cuda")
+        if named:
+            eng.set_grad_arena(arena, stride, 2)
+        for skip in (False, True):
+            if skip:
+                arena.fill_(1.0)
+                eng.grad[:cnt].copy_(to_dev(g[off:]))
+                eng.grad[5] = float("inf")
+            hp = OptStep.hyper(lr=3e-4, t=3, beta2=0.95, wd=0.1, clip=1.0)
+            eng.norm(hp)
+            eng.update(hp)
+            st = eng.status()
+            assert st.error == 0 and bool(st.skipped) == skip
+            if named:
+                assert not bool(arena.any())                   # every element of both parts
+                assert bool(eng.grad[:cnt].any())              # the reduced shard is scratch: left alone
+            else:
+                assert bool((arena == 1).all()) and not bool(eng.grad[:cnt].any())
+        outs.append([to_host(x[:cnt]).copy() for x in (eng.master, eng.m, eng.v, eng.twin_bf16)])
+        with pytest.raises(AnniError):
+            eng.set_grad_arena(arena, cnt - 8, 2)              # parts shorter than the shard
+        eng.close()
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+def test_fp8_step_in_one_launch_equals_the_other_forms(monkeypatch):
+    """e4m3 twins, one launch: the quantiser that follows the update tensor by tensor must give
+    the same bits as the older form (a quantise phase after a second grid barrier) and as the
+    three-launch form.  Shapes with tensors of several million elements, so that blocks wait for,
+    report and quantise tensors many rounds apart; two steps in a row reuse the counters."""
+    segs = lm_segments(d_model=512, d_ff=6144, n_blocks=2, vocab=1000, tied=True, wd="matrices", twin="fp8")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=9, grad_dtype=DT_BF16, state_dtype=DT_BF16)
+    _, g2, _, _ = make_inputs(n, seed=10, grad_dtype=DT_BF16, state_dtype=DT_BF16)
+    outs = []
+    for form in ("pipe", "barrier", "split"):
+        monkeypatch.setenv("ANNI_B200_FP8_PIPE", "0" if form == "barrier" else "1")
+        eng = _engine(segs, DT_BF16, DT_BF16, p, g, m, v)
+        for t, grads in ((5, g), (6, g2)):
+            eng.grad.copy_(to_dev(grads))
+            hp = OptStep.hyper(lr=3e-4, t=t, beta2=0.95, wd=0.1, clip=1.0)
+            (eng.step_split if form == "split" else eng.step)(hp)
+            st = eng.status()
+            assert st.error == 0 and st.skipped == 0
+        assert bool(eng.twin_fp8.any())
+        outs.append([to_host(x).copy() for x in (eng.master, eng.m, eng.v, eng.twin_bf16, eng.twin_fp8)]
+                    + [eng.scale_tensor().cpu().numpy().copy(), eng.amax_tensor().cpu().numpy().copy()])
+        eng.close()
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert np.array_equal(a, b)

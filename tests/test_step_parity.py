@@ -3,8 +3,10 @@ import numpy as np
 import pytest
 
 from anni_b200.capi import DT_BF16, DT_F32, SEG_TWIN_BF16, SEG_WD
-from anni_b200.engine import Segments, lm_segments, LM_SHAPES
-from parity_util import (bf16_bits_from_f32, check_step, make_inputs, run_gpu)
+import torch
+
+from anni_b200.engine import OptStep, Segments, lm_segments, LM_SHAPES
+from parity_util import (bf16_bits_from_f32, check_step, make_inputs, run_gpu, to_dev, to_host)
 
 pytestmark = pytest.mark.gpu
 
@@ -310,3 +312,38 @@ def test_transposed_fp8_twins_whole_and_edge_tiles(oracle):
         got = ft[aux[i].fp8_t_off:aux[i].fp8_t_off + r * c].reshape(c, r)
         assert np.array_equal(got, q.reshape(r, c).T), (r, c)
     eng.close()
+
+
+def test_step_with_sumsq_from_the_producer(oracle):
+    """anni_optstep_step_with_sumsq: the gradient producer hands over {sum of squares, non-finite
+    count} on the device, the step reads the gradients once.  Same bits as the one-launch step
+    that computes the norm itself; a non-finite count skips the step."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices", twin="fp8")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=66, grad_dtype=DT_BF16, state_dtype=DT_BF16)
+    hp = OptStep.hyper(lr=3e-4, t=9, beta2=0.95, wd=0.1, clip=1.0)
+    outs = []
+    for handed in (False, True):
+        eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_BF16).allocate()
+        for t, src in ((eng.master, p), (eng.grad, g), (eng.m, m), (eng.v, v)):
+            t.copy_(to_dev(src))
+        if handed:
+            ss = torch.stack([eng.grad.double().square().sum(), torch.zeros((), dtype=torch.float64, device="cuda")])
+            eng.step_with_sumsq(hp, ss)
+        else:
+            eng.step(hp)
+        st = eng.status()
+        assert st.error == 0 and st.skipped == 0
+        outs.append((st.norm, [to_host(x).copy() for x in (eng.master, eng.m, eng.v, eng.twin_bf16, eng.twin_fp8, eng.grad)]))
+        if handed:
+            eng.grad.copy_(to_dev(g))
+            before = eng.master.clone()
+            eng.step_with_sumsq(hp, torch.tensor([1.0, 3.0], dtype=torch.float64, device="cuda"))
+            st = eng.status()
+            assert st.skipped == 1 and torch.equal(eng.master, before) and not bool(eng.grad.any())
+        eng.close()
+    # the producer's sum (torch, another order) differs from the kernel's in the last bits only
+    assert abs(outs[0][0] - outs[1][0]) <= 1e-12 * outs[0][0]
+    for a, b in zip(outs[0][1], outs[1][1]):
+        same = (a == b).mean()
+        assert same > 0.999, same

@@ -22,24 +22,29 @@ def _world():
     return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 0
 
 
-@pytest.mark.parametrize("mode", ["mc", "peer", "copy", "nccl"])
+@pytest.mark.parametrize("mode", ["mc", "peer", "copy", "nccl", "peer_py", "nccl_py"])
 @pytest.mark.parametrize("twin,state", [("bf16", "f32"), ("bf16", "bf16"), ("fp8", "f32")])
 def test_zero1_matches_oracle_on_reduced_gradients(oracle, tmp_path, twin, state, mode):
     """mc: reduce-scatter and all-gather fused into the kernels through NVSwitch multicast
     (multimem.ld_reduce / multimem.st); peer: the same with plain peer loads / stores;
     copy: copy engines pull the gradient shards and push the twins, the kernels work on local memory;
-    nccl: the same step around NCCL reduce-scatter / all-gather."""
+    nccl: the same step around NCCL reduce-scatter / all-gather.  mc, peer and nccl run the step
+    sequence inside the library (anni_zero1_step, with a communicator of its own); the _py variants
+    run the same sequence from Python over torch.distributed.  In every mode the gradients are
+    accumulated into the arenas, which the step must therefore leave zeroed."""
     world = _world()
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ANNI_TEST_MODE=mode)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ANNI_TEST_MODE=mode.split("_")[0],
+               ANNI_B200_ZERO1_DRIVER="py" if mode.endswith("_py") else "c")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300),
            os.path.join(ROOT, "tests", "zero1_gpu_worker.py"), str(tmp_path), twin, state]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stderr[-3000:]
     z = np.load(tmp_path / f"zero1_gpu_{twin}_{state}.npz")
-    assert int(z["peer"]) == int(mode != "nccl")
+    assert int(z["peer"]) == int(not mode.startswith("nccl"))
+    assert str(z["driver"]) == ("python" if mode.endswith("_py") or mode == "copy" else "library")
     assert int(z["ckpt_round_trip"]) == 1
     if mode != "mc":
         assert int(z["multicast"]) == 0

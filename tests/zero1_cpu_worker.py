@@ -102,7 +102,8 @@ def main():
         if step == 2:
             base[n // 2] = np.inf                           # third step must be skipped on every rank
         gb = torch.from_numpy(base).to(torch.bfloat16)
-        z.grad_full[:n].copy_((gb.float() * (0.5 if world > 1 else 1.0)).to(torch.bfloat16))
+        assert not bool(z.grad_full.any())                  # the previous step left the whole arena zeroed
+        z.grad_full[:n] += (gb.float() * (0.5 if world > 1 else 1.0)).to(torch.bfloat16)
         hp = Hyper(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0,
                    grad_scale=1.0, t=step + 1)
         z.step(hp)

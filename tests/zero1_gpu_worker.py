@@ -45,13 +45,15 @@ def main():
         if step == 2:
             base[n - 7] = np.inf                                # lands in the LAST rank's shard only
         gb = torch.from_numpy(base).to(torch.bfloat16)
-        z.grad_full.zero_()
-        # every rank contributes g / world with world a power of two: the bf16 sum is exact
-        z.grad_full[:n].copy_((gb.float() / world).to(torch.bfloat16).to(dev))
+        # every rank contributes g / world with world a power of two: the bf16 sum is exact.  The
+        # gradients are ACCUMULATED into the arena, as a backward pass does (beta = 1 GEMMs): right
+        # only if the previous step left the whole arena zeroed, padding included.
+        z.grad_full[:n] += (gb.float() / world).to(torch.bfloat16).to(dev)
         hp = OptStep.hyper(lr=3e-4, t=step + 1, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0)
         z.step(hp)
         st = z.status()
-        stats.append((st.norm, st.skipped, st.error))
+        arena_clean = not bool(z.grad_full.any())            # also after the skipped step
+        stats.append((st.norm, st.skipped, st.error if arena_clean else -99))
     full_p = z.gather_full(z.master)
     full_m = z.gather_full(z.m)
     full_v = z.gather_full(z.v)
@@ -73,11 +75,12 @@ def main():
     all_stats = [None] * world
     dist.all_gather_object(all_stats, stats)
     if rank == 0:
-        np.savez(os.path.join(out_dir, f"zero1_gpu_{twin}_{state}.npz"), peer=int(z.peer), multicast=int(getattr(z, "uses_multicast", False)), p=to_host(full_p), m=to_host(full_m),
+        np.savez(os.path.join(out_dir, f"zero1_gpu_{twin}_{state}.npz"), peer=int(z.peer), driver=z.driver, multicast=int(getattr(z, "uses_multicast", False)), p=to_host(full_p), m=to_host(full_m),
                  v=to_host(full_v), twin=to_host(z.twin_full[:n]),
                  twin8=to_host(z.twin8_full[:n]) if z.twin8_full is not None else np.zeros(1, np.uint8),
                  scale=z.eng.scale_tensor().cpu().numpy(), stats=np.array(all_stats, dtype=np.float64),
                  world=world, ckpt_round_trip=int(ck_ok.item()))
+    z.close()
     dist.destroy_process_group()
 
 
