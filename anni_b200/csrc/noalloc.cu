@@ -215,7 +215,7 @@ extern "C" int anni_optstep_step_noalloc(const anni_optstep_config *cfg,
 	la.sc_log2 = d->sc_log2;
 	la.pipe_lag = ANNI_PIPE_LAG;
 	la.ctl = &d->ptr->ctl;
-	la.flags = has_fp8 ? (ANNI_LAUNCH_HAS_FP8 | ANNI_LAUNCH_FP8_PIPE) : 0;
+	la.flags = has_fp8 ? ANNI_LAUNCH_HAS_FP8 : 0;
 	rc = anni_fill_hyper(&la, hp);
 	if (rc != ANNI_OK)
 		return rc;

@@ -114,49 +114,6 @@ __device__ __forceinline__ float rcp_approx_ftz(float x)
 	return r;
 }
 
-/*
-** (double)x built with integer instructions instead of the conversion unit.  B200 converts
-** 16 values per clock and SM (the same unit runs the square roots and reciprocals), which
-** makes conversions, not memory, the limit of the norm pass and of the double-precision
-** update; shifts and adds run four to eight times as wide.  A normal float widens by
-** re-biasing the exponent (+896) and moving the mantissa up 29 bits; zero keeps its sign;
-** subnormals, infinities and NaNs (rare) take the hardware conversion.  Bit-identical to
-** (double)x for every input.
-*/
-__device__ __forceinline__ double widen_alu(float x)
-{
-	const uint32_t b = __float_as_uint(x);
-	const uint32_t a = b & 0x7fffffffu;
-	const bool normal = a - 0x00800000u < 0x7f000000u;
-
-	if (normal || a == 0u)
-		return __hiloint2double((int)((b & 0x80000000u) | ((a >> 3) + (normal ? 0x38000000u : 0u))),
-		    (int)(b << 29));
-	return (double)x;
-}
-
-/* (double)x by whichever route the build assigns to this use (bit k of `mask`) */
-template <int MASK, int BIT>
-__device__ __forceinline__ double widen(float x)
-{
-	return (MASK >> BIT) & 1 ? widen_alu(x) : (double)x;
-}
-
-/*
-** x rounded to 24 significant bits, still a double: Veltkamp's split with 2^29 + 1.  For x
-** inside the float range this is (double)(float)x -- computed in the double-precision pipe
-** instead of a narrowing and a widening conversion -- except that a value exactly half way
-** between two floats (one in 2^29) may round to either neighbour.  The exact update uses it
-** for the operands of the update term only; what is STORED is always rounded by the
-** conversion proper.
-*/
-__device__ __forceinline__ double round_to_24_bits(double x)
-{
-	const double c = __dmul_rn(x, 536870913.0);
-
-	return __dsub_rn(c, __dsub_rn(c, x));
-}
-
 __device__ __forceinline__ f32x8 unpack_bf16x8(uint4 q)
 {
 	f32x8 r;
@@ -483,9 +440,8 @@ __device__ __forceinline__ void norm_accumulate(const f32x8 &g, double &acc0, do
 	** agree with a double accumulation to the last bits */
 #pragma unroll
 	for (int k = 0; k < ANNI_VEC; k += 2) {
-		/* the widenings are shared out between the conversion unit and the integer pipe */
-		const double g0 = k < ANNI_NORM_ALU_LANES ? widen_alu(g.x[k]) : (double)g.x[k];
-		const double g1 = k + 1 < ANNI_NORM_ALU_LANES ? widen_alu(g.x[k + 1]) : (double)g.x[k + 1];
+		const double g0 = (double)g.x[k];
+		const double g1 = (double)g.x[k + 1];
 
 		acc0 = fma(g0, g0, acc0);
 		acc1 = fma(g1, g1, acc1);
@@ -581,10 +537,9 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	float gf, float &p, float &m, float &v)
 {
 	/* moments: the reference's double expression, each product and the sum rounded on its own */
-	constexpr int W = EXACT ? ANNI_WIDEN_EXACT : ANNI_WIDEN_FAST;
-	const double g = __dmul_rn(widen<W, 0>(gf), coef);
-	const double md = __dadd_rn(__dmul_rn(a.b1, widen<W, 1>(m)), __dmul_rn(a.omb1, g));
-	const double vd = __dadd_rn(__dmul_rn(a.b2, widen<W, 2>(v)), __dmul_rn(__dmul_rn(a.omb2, g), g));
+	const double g = __dmul_rn((double)gf, coef);
+	const double md = __dadd_rn(__dmul_rn(a.b1, (double)m), __dmul_rn(a.omb1, g));
+	const double vd = __dadd_rn(__dmul_rn(a.b2, (double)v), __dmul_rn(__dmul_rn(a.omb2, g), g));
 
 	m = __double2float_rn(md);
 	v = __double2float_rn(vd);
@@ -603,9 +558,7 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 		** (relative error ~1e-12), so p - u rounds to the reference's float in
 		** all but about one element in ten million.
 		*/
-		/* the rounded moments as doubles, without going through the conversion unit twice */
-		const double vr = ANNI_EXACT_SPLIT ? round_to_24_bits(vd) : (double)v;
-		const double mr = ANNI_EXACT_SPLIT ? round_to_24_bits(md) : (double)m;
+		const double vr = (double)v;
 		const double x = vr * a.ibc2d;
 		const double hx = vr * (0.5 * a.ibc2d);
 		double y;
@@ -617,15 +570,10 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 
 		asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(q) : "d"(dn));
 		q = fma(fma(-dn, q, 1.0), q, q);
-		const double pd = widen<W, 3>(p) - (a.lrbc1d * mr) * q;
+		const float p1 = __double2float_rn((double)p - (a.lrbc1d * (double)m) * q);
 
 		/* decay on the stored float, in double as the reference does, rounded once */
-		if (lrwd != 0.0f) {
-			const double p1 = ANNI_EXACT_SPLIT ? round_to_24_bits(pd) : (double)__double2float_rn(pd);
-
-			p = __double2float_rn(fma(-a.lrwdd, p1, p1));
-		} else
-			p = __double2float_rn(pd);
+		p = lrwd != 0.0f ? __double2float_rn(fma(-a.lrwdd, (double)p1, (double)p1)) : p1;
 		return;
 	}
 	/*
@@ -838,11 +786,15 @@ __device__ __forceinline__ void store_e4m3x4(const anni_launch &a, uint64_t e, u
 ** need its amax, i.e. every block must have finished updating it; re-reading its fresh
 ** master from HBM afterwards costs 4 bytes per element.  So each block reports a tensor as
 ** soon as its own (descending) walk has left it behind -- after flushing its amax share --
-** and, a little later, quantises its share of that tensor: by then the whole grid has
-** reported it (the blocks move in step), the per-tensor wait ends at once, and the master
-** lines written minutes of nanoseconds ago are still in the 126 MB L2 (they are stored with
-** the default policy; everything else streams through with evict-first hints).  The wait is
-** bounded like the grid barrier and gives up at once when any block has raised an error.
+** and from then on slips a little of that tensor's quantising in after every super-chunk it
+** updates: one trip of four chunks per round, two while it has a backlog.  The quantiser's
+** loads hit the 126 MB L2 (the masters of such tensors are stored with the default policy,
+** everything else streams through with evict-first hints; measured: 89 % of them), and because
+** they are spread over the update's rounds they overlap its HBM traffic instead of replacing
+** it.  Nobody waits inside the walk: a tensor that the rest of the grid has not left yet is
+** simply tried again next round.  Only after its last super-chunk does a block wait for the
+** tensors still open, with the same bound as the grid barrier, giving up at once when any
+** block has raised an error.
 */
 __device__ __forceinline__ bool pipe_wants(const anni_launch &a, int s)
 {
@@ -861,27 +813,59 @@ __device__ __forceinline__ void pipe_report(const anni_launch &a, int s)
 	}
 }
 
-/* this block's share of tensor s's e4m3 codes; false when the wait for the other blocks gave up */
-__device__ __forceinline__ bool pipe_quantize(const anni_launch &a, int s)
-{
-	__shared__ int s_ok;
+/* the tensor a block is quantising its share of (all fields block-uniform) */
+struct pipe_state {
+	uint64_t	c;	/* this block's next chunk of the tensor */
+	uint64_t	c_hi;	/* one past the tensor's last chunk */
+	uint64_t	lo;	/* the tensor inside the shard: elements [lo, hi) */
+	uint64_t	hi;
+	float		inv;	/* 1 / scale, once the tensor is complete */
+	int		s;	/* tensor, or -1: none open */
+	bool		ready;	/* every block has reported it; inv is valid */
+};
 
+/* opens tensor s; false when there is nothing to quantise in it for anybody in this shard */
+__device__ __forceinline__ bool pipe_open(const anni_launch &a, int s, pipe_state &q)
+{
 	if (!pipe_wants(a, s))
-		return true;
+		return false;
 	const int64_t t_lo = max(a.seg_off[s], (int64_t)a.arena_off) - (int64_t)a.arena_off;
 	const int64_t t_hi = min(a.seg_off[s + 1], (int64_t)(a.arena_off + a.n)) - (int64_t)a.arena_off;
 
 	if (t_lo >= t_hi)
-		return true;		/* not in this shard */
+		return false;
+	q.s = s;
+	q.ready = false;
+	q.lo = (uint64_t)t_lo;
+	q.hi = (uint64_t)t_hi;
+	q.c = (q.lo >> ANNI_UCHUNK_LOG2) + blockIdx.x;
+	q.c_hi = (q.hi + ANNI_UCHUNK - 1) >> ANNI_UCHUNK_LOG2;
+	return true;
+}
+
+/*
+** Has the whole grid reported the open tensor?  1: yes (q.inv set), 0: not yet (only when
+** `wait` is false), -1: the bounded wait gave up.  Block-uniform; one block-wide
+** synchronisation per call.
+*/
+__device__ __forceinline__ int pipe_poll(const anni_launch &a, pipe_state &q, bool wait)
+{
+	__shared__ int s_state;
+
 	__syncthreads();
 	if (threadIdx.x == 0) {
 		uint32_t polls = 0;
-		int ok = 1;
+		int state = 1;
 
-		while (ld_acquire_u32(&a.seg_done[s]) < gridDim.x) {
+		while (ld_acquire_u32(&a.seg_done[q.s]) < gridDim.x) {
+			if (!wait) {
+				state = 0;
+				break;
+			}
 			__nanosleep(32);
-			if (++polls > ANNI_WAIT_POLLS || ld_acquire_u32(reinterpret_cast<const uint32_t *>(&a.ctl->error)) != 0) {
-				ok = 0;
+			if (++polls > ANNI_WAIT_POLLS
+			    || ld_acquire_u32(reinterpret_cast<const uint32_t *>(&a.ctl->error)) != 0) {
+				state = -1;
 				atomicCAS(&a.ctl->error, 0, ANNI_E_BARRIER_TIMEOUT);
 				break;
 			}
@@ -889,52 +873,91 @@ __device__ __forceinline__ bool pipe_quantize(const anni_launch &a, int s)
 		if (polls)
 			atomicAdd(&a.ctl->pipe_polls, polls);
 		__threadfence();
-		s_ok = ok;
+		s_state = state;
 	}
 	__syncthreads();
-	if (!s_ok)
-		return false;
-	const float scale = fp8_scale(__ldcg(&a.seg_amax[s]));
-	const float inv = __fdiv_rn(1.0f, scale);
-	const uint64_t lo = (uint64_t)t_lo;
-	const uint64_t hi = (uint64_t)t_hi;
-	const uint64_t c_hi = (hi + ANNI_UCHUNK - 1) >> ANNI_UCHUNK_LOG2;
+	const int state = s_state;
+
+	if (state == 1) {
+		const float scale = fp8_scale(__ldcg(&a.seg_amax[q.s]));
+
+		q.inv = __fdiv_rn(1.0f, scale);
+		q.ready = true;
+		if (blockIdx.x == 0 && threadIdx.x == 0)
+			a.seg_scale[q.s] = scale;
+	}
+	return state;
+}
+
+/* one trip: up to four of this block's chunks of the open tensor; true when the tensor is finished */
+__device__ __forceinline__ bool pipe_trip(const anni_launch &a, pipe_state &q)
+{
 	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
 	const uint64_t G = gridDim.x;
+	const uint64_t c = q.c;
 
-	if (blockIdx.x == 0 && threadIdx.x == 0)
-		a.seg_scale[s] = scale;
-	for (uint64_t c = (lo >> ANNI_UCHUNK_LOG2) + blockIdx.x; c < c_hi; c += 4 * G) {
-		/* four chunks per trip, their loads issued together */
-		if (a.aligned && (c << ANNI_UCHUNK_LOG2) >= lo && ((c + 3 * G + 1) << ANNI_UCHUNK_LOG2) <= hi) {
-			const uint64_t e0 = (c << ANNI_UCHUNK_LOG2) + t4;
-			const uint64_t st = G << ANNI_UCHUNK_LOG2;
-			const f32x4 p0 = io4<float>::load(a.master, e0);
-			const f32x4 p1 = io4<float>::load(a.master, e0 + st);
-			const f32x4 p2 = io4<float>::load(a.master, e0 + 2 * st);
-			const f32x4 p3 = io4<float>::load(a.master, e0 + 3 * st);
+	if (c >= q.c_hi)
+		return true;
+	q.c = c + 4 * G;
+	/* four whole chunks: their loads issued together */
+	if (a.aligned && (c << ANNI_UCHUNK_LOG2) >= q.lo && ((c + 3 * G + 1) << ANNI_UCHUNK_LOG2) <= q.hi) {
+		const uint64_t e0 = (c << ANNI_UCHUNK_LOG2) + t4;
+		const uint64_t st = G << ANNI_UCHUNK_LOG2;
+		const f32x4 p0 = io4<float>::load(a.master, e0);
+		const f32x4 p1 = io4<float>::load(a.master, e0 + st);
+		const f32x4 p2 = io4<float>::load(a.master, e0 + 2 * st);
+		const f32x4 p3 = io4<float>::load(a.master, e0 + 3 * st);
 
-			store_e4m3x4(a, e0, e4m3x4(p0, inv));
-			store_e4m3x4(a, e0 + st, e4m3x4(p1, inv));
-			store_e4m3x4(a, e0 + 2 * st, e4m3x4(p2, inv));
-			store_e4m3x4(a, e0 + 3 * st, e4m3x4(p3, inv));
+		store_e4m3x4(a, e0, e4m3x4(p0, q.inv));
+		store_e4m3x4(a, e0 + st, e4m3x4(p1, q.inv));
+		store_e4m3x4(a, e0 + 2 * st, e4m3x4(p2, q.inv));
+		store_e4m3x4(a, e0 + 3 * st, e4m3x4(p3, q.inv));
+		return q.c >= q.c_hi;
+	}
+	for (int k = 0; k < 4; k++) {
+		const uint64_t ck = c + (uint64_t)k * G;
+		const uint64_t e = (ck << ANNI_UCHUNK_LOG2) + t4;
+
+		if (ck >= q.c_hi)
+			break;
+		if (a.aligned && (ck << ANNI_UCHUNK_LOG2) >= q.lo && ((ck + 1) << ANNI_UCHUNK_LOG2) <= q.hi) {
+			store_e4m3x4(a, e, e4m3x4(io4<float>::load(a.master, e), q.inv));
 			continue;
 		}
-		for (int k = 0; k < 4; k++) {
-			const uint64_t ck = c + (uint64_t)k * G;
-			const uint64_t e = (ck << ANNI_UCHUNK_LOG2) + t4;
+		for (int j = 0; j < ANNI_UVEC; j++)	/* the tensor's ragged ends, its own elements only */
+			if (e + j >= q.lo && e + j < q.hi)
+				a.twin8[e + j] = (uint8_t)__nv_cvt_float_to_fp8(a.master[e + j] * q.inv,
+				    __NV_SATFINITE, __NV_E4M3);
+	}
+	return q.c >= q.c_hi;
+}
 
-			if (ck >= c_hi)
-				break;
-			if (a.aligned && (ck << ANNI_UCHUNK_LOG2) >= lo && ((ck + 1) << ANNI_UCHUNK_LOG2) <= hi) {
-				store_e4m3x4(a, e, e4m3x4(io4<float>::load(a.master, e), inv));
+/*
+** Up to `trips` trips on the tensors this block has reported down to (not including) rep_hi,
+** highest first.  wait = false: a tensor the grid has not finished is left for the next call.
+** False when a bounded wait gave up.
+*/
+__device__ __forceinline__ bool pipe_work(const anni_launch &a, pipe_state &q, int &q_hi, int rep_hi,
+	int trips, bool wait)
+{
+	while (trips > 0) {
+		if (q.s < 0) {
+			if (q_hi <= rep_hi)
+				return true;		/* nothing reported that is still to do */
+			if (!pipe_open(a, q_hi--, q))
 				continue;
-			}
-			for (int j = 0; j < ANNI_UVEC; j++)	/* the tensor's ragged ends, its own elements only */
-				if (e + j >= lo && e + j < hi)
-					a.twin8[e + j] = (uint8_t)__nv_cvt_float_to_fp8(a.master[e + j] * inv,
-					    __NV_SATFINITE, __NV_E4M3);
 		}
+		if (!q.ready) {
+			const int state = pipe_poll(a, q, wait);
+
+			if (state < 0)
+				return false;
+			if (state == 0)
+				return true;		/* not complete yet: next round */
+		}
+		if (pipe_trip(a, q))
+			q.s = -1;
+		trips--;
 	}
 	return true;
 }
@@ -952,12 +975,17 @@ __device__ __forceinline__ bool update_phase(const anni_launch &a, const decisio
 	const uint64_t t4 = (uint64_t)threadIdx.x * ANNI_UVEC;
 	const uint32_t per = 1u << w.sc;			/* chunks per super-chunk */
 	const uint64_t span = (uint64_t)ANNI_UCHUNK << w.sc;	/* elements per super-chunk */
-	const int64_t lag = (int64_t)(gridDim.x * span) * (a.pipe_lag > 0 ? a.pipe_lag : 1);	/* PIPE: rounds of the whole grid */
 	float tmax = 0.0f;
 	int seg = -1;
 	int amax_seg = -1;
 	int rep_hi = a.n_seg - 1;	/* PIPE: highest tensor this block has not reported yet */
-	int q_hi = a.n_seg - 1;		/* PIPE: highest tensor this block has not quantised its share of */
+	int q_hi = a.n_seg - 1;		/* PIPE: highest tensor this block has not opened for quantising yet */
+	pipe_state q;
+
+	q.s = -1;
+	q.ready = false;
+	q.c = q.c_hi = q.lo = q.hi = 0;
+	q.inv = 0.0f;
 
 	if (d.skip && !(a.flags & ANNI_STEP_ZERO_GRAD))
 		return true;
@@ -979,9 +1007,10 @@ __device__ __forceinline__ bool update_phase(const anni_launch &a, const decisio
 				}
 				pipe_report(a, rep_hi--);
 			}
-			while (q_hi > rep_hi && a.seg_off[q_hi] >= top + lag)
-				if (!pipe_quantize(a, q_hi--))
-					return false;
+			/* a little quantising per round; more while further tensors are waiting behind the open one */
+			if ((q.s >= 0 || q_hi > rep_hi)
+			    && !pipe_work(a, q, q_hi, rep_hi, q_hi - rep_hi >= 2 ? a.pipe_lag : 1, false))
+				return false;
 		}
 		if (seg < 0)
 			seg = seg_find(a.seg_off, a.n_seg, alo);
@@ -1023,8 +1052,8 @@ __device__ __forceinline__ bool update_phase(const anni_launch &a, const decisio
 		/* the walk is over: report what is left, then quantise what is left */
 		while (rep_hi >= 0)
 			pipe_report(a, rep_hi--);
-		while (q_hi >= 0)
-			if (!pipe_quantize(a, q_hi--))
+		while (q.s >= 0 || q_hi >= 0)
+			if (!pipe_work(a, q, q_hi, -1, 1 << 20, true))
 				return false;
 	}
 	return true;

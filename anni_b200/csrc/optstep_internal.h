@@ -24,31 +24,8 @@
 #define ANNI_UVEC		4
 #define ANNI_UCHUNK		(ANNI_THREADS * ANNI_UVEC)
 #define ANNI_UCHUNK_LOG2	10
-/*
-** How the float -> double widenings are shared between the conversion unit (16 per clock and
-** SM on B200, also busy with square roots, reciprocals and the narrowing conversions) and the
-** integer pipe (see widen_alu in optstep.cu).  Results do not depend on these.
-**   ANNI_NORM_ALU_LANES  of the eight gradients of a vector, how many the norm phase widens
-**                        with integer instructions
-**   ANNI_WIDEN_FAST / ANNI_WIDEN_EXACT  bit 0: gradient, 1: m, 2: v, 3: master -- widened
-**                        with integer instructions in the fast / exact update
-**   ANNI_EXACT_SPLIT     exact update: take the rounded moments' doubles from a Veltkamp split
-**                        instead of converting the stored floats back
-*/
-#ifndef ANNI_NORM_ALU_LANES
-#define ANNI_NORM_ALU_LANES	0
-#endif
-#ifndef ANNI_WIDEN_FAST
-#define ANNI_WIDEN_FAST		0
-#endif
-#ifndef ANNI_WIDEN_EXACT
-#define ANNI_WIDEN_EXACT	0
-#endif
 #ifndef ANNI_PIPE_LAG
-#define ANNI_PIPE_LAG		1	/* default of anni_launch.pipe_lag */
-#endif
-#ifndef ANNI_EXACT_SPLIT
-#define ANNI_EXACT_SPLIT	1
+#define ANNI_PIPE_LAG		2	/* default of anni_launch.pipe_lag */
 #endif
 /* tile of the transposed e4m3 twins: rows x columns of the master (kernel and host tile count) */
 #define ANNI_TT_R		128
@@ -105,7 +82,7 @@ typedef struct anni_launch {
 	int		flags;		/* ANNI_STEP_* | ANNI_LAUNCH_* */
 	int		aligned;	/* every buffer 16-byte aligned: vector path allowed */
 	int		sc_log2;	/* log2 of the chunks per super-chunk (see walk_chunk) */
-	int		pipe_lag;	/* one-launch fp8 step: rounds of the grid between leaving a tensor and quantising it */
+	int		pipe_lag;	/* one-launch fp8 step: quantising trips per round while tensors queue up (else one) */
 	double		grad_scale;
 	double		clip;
 	double		b1;

@@ -393,7 +393,8 @@ class CompressibleArena:
     """A zeroed device buffer in compressible memory (anni_arena_alloc) seen as a torch tensor.
     Meant for the gradient arena, which every step leaves zeroed: the L2 writes zero lines back
     at a fraction of their size.  Raises capi.AnniError(E_LIMIT) where the device has no such
-    memory; keep the object alive as long as the tensor is in use."""
+    memory.  The mapping is released by ``close()`` only -- never behind the back of a tensor or
+    slice that may still point into it; an arena that is never closed lives until the process ends."""
 
     def __init__(self, n, dtype, device="cuda"):
         self.L = capi.lib()
@@ -413,16 +414,12 @@ class CompressibleArena:
         self.tensor = t if t.dtype == dtype else t.view(dtype)
 
     def close(self):
+        """Unmaps the arena (synchronises the device first).  The caller vouches that no tensor or
+        slice of it is used afterwards."""
         if getattr(self, "ptr", None):
             self.tensor = None
             self.L.anni_arena_free(self.ptr, self.mapped_bytes)
             self.ptr = None
-
-    def __del__(self):
-        try:
-            self.close()
-        except Exception:
-            pass
 
 
 def kernel_launches():

@@ -361,6 +361,7 @@ def zero1_parity_check(dev, rank, world, zero1_kwargs):
         problems.append(f"sharded state against the oracle: {e}")
     if not np.array_equal(to_host(z.twin_full[:n]), bf16_bits_from_f32(gp)):
         problems.append("all-gathered twins are not the RNE cast of the master")
+    z.close()
     del z
 
     segs4 = lm_segments(**LM_SHAPES["synth3b"], wd="matrices")
@@ -706,6 +707,8 @@ def run_ours(args):
                  "path": "anni_lm_adam_step_scaled: upload of pinned host fp32 gradients (147 tensors), "
                          "one-launch step, status read, host gradients zeroed"}
 
+    driver_name = z.driver
+    z.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -767,7 +770,7 @@ def run_ours(args):
         wire = (world - 1) / world * n * 2 / 1e9            # GB each way per GPU, per collective
         rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
         ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
-        line["nvlink"] = {"driver": z.driver, "mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
+        line["nvlink"] = {"driver": driver_name, "mode": ("peer kernels, NVSwitch multicast" if getattr(z, "uses_multicast", False)
                                    else "copy engines + local kernels" if getattr(z, "copy_mode", False)
                                    else "peer kernels" if z.peer else "nccl"), "wire_gb_per_collective": wire,
                           "link_gbs": 770.0, "floor_ms_per_collective": wire / 770.0 * 1e3,

@@ -142,9 +142,10 @@ int	anni_optstep_bind(anni_optstep *h, const anni_optstep_buffers *buf);
 /*
 ** Whole step in ONE cooperative launch on `stream` (a cudaStream_t, NULL = the
 ** legacy stream): norm phase, device-wide bounded barrier, decision, update
-** phase, twin emission; for fp8 segments the quantiser follows the update tensor
-** by tensor inside the same phase (each tensor's codes are written as soon as the
-** whole grid has left it, while its fresh master is still in L2).  Replaces the reference sequence gpu_grad_sumsq -> host
+** phase, twin emission, and for fp8 segments a second barrier and the quantising
+** phase (preceded by one small memset of the per-tensor amax table; with
+** ANNI_B200_FP8_PIPE=1 the quantiser instead follows the update tensor by tensor
+** inside the same phase and the memset goes away).  Replaces the reference sequence gpu_grad_sumsq -> host
 ** sqrt/clip/skip -> gpu_adam_step_dev_bf16 (lang/lm_adam.c:466-493) and its two
 ** host round trips.  Single-GPU form: the norm is this shard's alone.
 */

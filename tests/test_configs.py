@@ -257,3 +257,95 @@ def test_config5_dynamic_loss_scale_and_skip_sequence(oracle):
         else:
             assert np.array_equal(t16[sl], bf16_bits_from_f32(gp[sl]))
     eng.close()
+
+
+def test_config2_full_size_two_steps_with_static_loss_scale(oracle):
+    """Configuration 2 at its own size: the 184,676,352-parameter shapes, bf16 gradients that carry
+    a static loss scale of 1024 (grad_scale = 1/1024), fp32 master and moments, bf16 twins, LR from
+    the warm-up / cosine schedule, the default (fast) update arithmetic.  Two consecutive steps
+    with fresh gradients; after each, the device state against the oracle's step from the same
+    previous state (the device state is then carried on, so the second step starts from what the
+    first one really left)."""
+    segs = lm_segments(**LM_SHAPES["talk170m"], wd="matrices")
+    n = segs.n
+    p, g, m, v = device_inputs(n, seed=21, grad_dtype=DT_BF16, state_dtype=DT_F32)
+    eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_F32).allocate()
+    eng.master.copy_(to_dev(p))
+    eng.m.copy_(to_dev(m))
+    eng.v.copy_(to_dev(v))
+    for t in (150, 151):
+        # gradients as the backward pass leaves them: multiplied by the loss scale, rounded to bf16
+        gs = to_host((to_dev(g).float() * (1024.0 if t == 150 else 768.0)).to(torch.bfloat16))
+        lr = schedule.lr_at(3e-4, t, 100, 1000, "cosine")
+        eng.grad.copy_(to_dev(gs))
+        eng.step(OptStep.hyper(lr=lr, t=t + 1, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0 / 1024))
+        st = eng.status()
+        ref = [x.copy() for x in (p, gs, m, v)]
+        info = oracle.step(*ref, lr=lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                           grad_scale=1.0 / 1024, t_before=t, check_finite=True,
+                           seg_off=segs.offsets, seg_flags=segs.flag_array)
+        assert st.error == 0 and st.skipped == 0 and not info["skipped"]
+        assert abs(st.norm - info["norm"]) <= 1e-9 * info["norm"] and st.norm > 1.0
+        out = dict(p=to_host(eng.master), m=to_host(eng.m), v=to_host(eng.v))
+        check_step_chunked(out, ref[0], ref[2], ref[3], p, exact_moments=False, m_old=m)
+        assert torch.equal(eng.twin_bf16, eng.master.to(torch.bfloat16))
+        assert not bool(eng.grad.any())
+        p, m, v = out["p"], out["m"], out["v"]          # carry the DEVICE state on
+    eng.close()
+
+
+def test_config5_full_size_fp8_twins_and_skip(oracle):
+    """Configuration 5 at its own size: 555,762,080 parameters, bf16 gradients carrying the dynamic
+    loss scale (65536), bf16 m/v, e4m3 twins with a per-tensor scale for the block matrices and bf16
+    twins elsewhere, one launch per step.  Step 1 is clean: state against the oracle, every e4m3
+    tensor against the oracle's quantiser applied to the GPU master (scale and codes bit for bit),
+    bf16 twins the RNE cast.  Step 2 carries an inf in one tensor: skipped, loss scale halved,
+    master, moments and twins untouched, gradients zeroed."""
+    segs = lm_segments(**LM_SHAPES["run555m"], wd="matrices", twin="fp8")
+    n = segs.n
+    p, g, m, v = device_inputs(n, seed=55, grad_dtype=DT_BF16, state_dtype=DT_BF16, grad_std=5e-4)
+    gs = to_host((to_dev(g).float() * 65536.0).to(torch.bfloat16))
+    del g
+    eng = OptStep(segs, grad_dtype=DT_BF16, state_dtype=DT_BF16).allocate()
+    eng.master.copy_(to_dev(p))
+    eng.m.copy_(to_dev(m))
+    eng.v.copy_(to_dev(v))
+    eng.grad.copy_(to_dev(gs))
+    eng.loss_scale_init(scale=65536.0, growth_interval=200)
+    hp = OptStep.hyper(lr=3e-4, t=1000, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0, dev_loss_scale=True)
+    eng.step(hp)
+    st = eng.status()
+    ref = [x.copy() for x in (p, gs, m, v)]
+    info = oracle.step(*ref, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0,
+                       grad_scale=1.0 / 65536.0, t_before=999, check_finite=True,
+                       seg_off=segs.offsets, seg_flags=segs.flag_array)
+    assert st.error == 0 and st.skipped == 0 and not info["skipped"]
+    assert abs(st.norm - info["norm"]) <= 1e-9 * info["norm"] and st.loss_scale == 65536.0 and st.good_steps == 1
+    out = dict(p=to_host(eng.master), m=to_host(eng.m), v=to_host(eng.v))
+    check_step_chunked(out, ref[0], ref[2], ref[3], p, exact_moments=False, m_old=m)
+    del ref
+    t8, t16, sc = to_host(eng.twin_fp8), to_host(eng.twin_bf16), eng.scale_tensor().cpu().numpy()
+    from anni_b200.capi import SEG_TWIN_FP8
+    off = segs.offsets
+    n8 = 0
+    for i in range(len(segs)):
+        sl = slice(int(off[i]), int(off[i + 1]))
+        if segs.flags[i] & SEG_TWIN_FP8:
+            amax, scale, q = oracle.fp8_quant(out["p"][sl])
+            assert np.float32(sc[i]) == np.float32(scale), segs.names[i]
+            assert np.array_equal(t8[sl], q), segs.names[i]
+            n8 += 1
+        else:
+            assert np.array_equal(t16[sl], bf16_bits_from_f32(out["p"][sl])), segs.names[i]
+    assert n8 == 6 * 14
+    # step 2: one tensor's gradient holds an inf
+    eng.grad.copy_(to_dev(gs))
+    eng.grad[segs.slice_of("blk7.w1").start + 12345] = float("inf")
+    before = [x.clone() for x in (eng.master, eng.m, eng.v, eng.twin_fp8, eng.twin_bf16)]
+    eng.step(OptStep.hyper(lr=3e-4, t=1001, beta2=0.95, wd=0.1, clip=1.0, grad_scale=1.0, dev_loss_scale=True))
+    st = eng.status()
+    assert st.error == 0 and st.skipped == 1 and st.loss_scale == 32768.0 and st.good_steps == 0
+    for a, b in zip(before, (eng.master, eng.m, eng.v, eng.twin_fp8, eng.twin_bf16)):
+        assert torch.equal(a, b)
+    assert not bool(eng.grad.any())
+    eng.close()

@@ -150,9 +150,9 @@ def test_update_clears_the_named_gradient_arena():
 
 
 def test_fp8_step_in_one_launch_equals_the_other_forms(monkeypatch):
-    """e4m3 twins, one launch: the quantiser that follows the update tensor by tensor must give
-    the same bits as the older form (a quantise phase after a second grid barrier) and as the
-    three-launch form.  Shapes with tensors of several million elements, so that blocks wait for,
+    """e4m3 twins, one launch: the optional form whose quantiser follows the update tensor by
+    tensor (ANNI_B200_FP8_PIPE=1) must give the same bits as the default one (a quantise phase
+    after a second grid barrier) and as the three-launch form.  Shapes with tensors of several million elements, so that blocks wait for,
     report and quantise tensors many rounds apart; two steps in a row reuse the counters."""
     segs = lm_segments(d_model=512, d_ff=6144, n_blocks=2, vocab=1000, tied=True, wd="matrices", twin="fp8")
     n = segs.n
@@ -160,7 +160,7 @@ def test_fp8_step_in_one_launch_equals_the_other_forms(monkeypatch):
     _, g2, _, _ = make_inputs(n, seed=10, grad_dtype=DT_BF16, state_dtype=DT_BF16)
     outs = []
     for form in ("pipe", "barrier", "split"):
-        monkeypatch.setenv("ANNI_B200_FP8_PIPE", "0" if form == "barrier" else "1")
+        monkeypatch.setenv("ANNI_B200_FP8_PIPE", "1" if form == "pipe" else "0")
         eng = _engine(segs, DT_BF16, DT_BF16, p, g, m, v)
         for t, grads in ((5, g), (6, g2)):
             eng.grad.copy_(to_dev(grads))
