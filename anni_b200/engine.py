@@ -137,6 +137,7 @@ LM_SHAPES = {
     "run555m": dict(d_model=1536, d_ff=6272, n_blocks=14, vocab=100000, tied=True),    # 555,762,080
     "synth3b": dict(d_model=2560, d_ff=10240, n_blocks=32, vocab=100000, tied=True),   # 2,773,419,680
     "tiny": dict(d_model=64, d_ff=256, n_blocks=2, vocab=300, tied=False),             # 138,156 (the reference's unit-test LM)
+    "blocks3": dict(d_model=1536, d_ff=6272, n_blocks=3, vocab=8000, tied=True),       # 98,452,160: run555m's blocks, a case sized for profiler captures
 }
 
 

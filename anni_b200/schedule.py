@@ -1,9 +1,10 @@
-"""LR schedule and loss-scale bookkeeping around the step (host side).
+"""The LR schedule the trainer evaluates before each step (host side).
 
 ``lr_at`` is the reference trainer's ``lm_train_step_lr`` (``lang/lm_train.c:98-124``),
 evaluated by the library's C function ``anni_lr_schedule`` so that Python and C callers get
 the same doubles.  The trainer calls it with ``opt->t`` BEFORE the step increments it
-(``lang/lm_train.c:1336``).
+(``lang/lm_train.c:1336``).  (The dynamic loss scale is not kept here: it lives on the device,
+``anni_optstep_loss_scale_init`` / ``OptStep.loss_scale_init``.)
 """
 import ctypes as C
 

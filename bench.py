@@ -42,6 +42,9 @@ WORKLOADS = {
     "talk170m-mixed": ("talk170m", "bf16", "f32", "bf16", 28),   # configuration 2
     "talk170m-fp32": ("talk170m", "f32", "f32", "bf16", 30),     # configuration 1 run on the GPU
     "synth3b": ("synth3b", "bf16", "f32", "bf16", 28),           # configuration 4 (8 GPUs)
+    # three of run555m's blocks and a small head, about 1 GB on the device: sized for profiler captures
+    "blocks3": ("blocks3", "bf16", "bf16", "bf16", 20),
+    "blocks3-fp8": ("blocks3", "bf16", "bf16", "fp8", 19),
 }
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1, clip=1.0)
 # DRAM bytes per parameter of the fused kernel: dram__bytes_read.sum + dram__bytes_write.sum of one
@@ -456,10 +459,10 @@ def run_ours(args):
     def bind_grads(arena):
         z.use_grad_arena(arena)
 
-    def hyper(t, exact=False):
+    def hyper(t, exact=False, zero_grad=True):
         return OptStep.hyper(lr=HYPER["lr"], t=t, beta1=HYPER["beta1"], beta2=HYPER["beta2"],
                              eps=HYPER["eps"], wd=HYPER["wd"], clip=HYPER["clip"],
-                             grad_scale=1.0 / world, check_finite=True, zero_grad=True, exact=exact)
+                             grad_scale=1.0 / world, check_finite=True, zero_grad=zero_grad, exact=exact)
 
     def barrier():
         if world > 1:
@@ -546,6 +549,18 @@ def run_ours(args):
         total_ms = float(tmax.item())
     ms_per_step = total_ms / K
     value = n / (ms_per_step * 1e-3)
+    if args.profile:
+        # a run for the profiler: the steps above and nothing else
+        if rank == 0:
+            print(json.dumps({"metric": "adam_step_params_per_s", "value": value, "unit": "params/s",
+                              "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+                              "config": {"workload": args.workload, "n_params": n}, "profile_run": True,
+                              "status": {"norm": st.norm, "skipped": int(st.skipped), "error": int(st.error)}}),
+                  flush=True)
+        z.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
 
     # ---- the same step with the parameter update evaluated in double (ANNI_STEP_EXACT_UPDATE) ----
     exact_ms = None
@@ -569,6 +584,30 @@ def run_ours(args):
         e1.record()
         barrier()
         exact_ms = e0.elapsed_time(e1) / k_ex
+
+    # ---- the same step without the gradient zeroing (a trainer whose first micro-batch overwrites) ----
+    # Not the contract's step: it shows what the 2 bytes per parameter of zeroing stores cost.
+    nozero_ms = None
+    if world == 1:
+        refill()
+        torch.cuda.synchronize()
+        time.sleep(1.0)
+        for i in range(2):
+            bind_grads(pool[i])
+            z.step(hyper(t, zero_grad=False))
+            t += 1
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        k_nz = min(10, pool_n - 2)
+        e0.record()
+        for i in range(k_nz):
+            bind_grads(pool[2 + i])
+            z.step(hyper(t, zero_grad=False))
+            t += 1
+        e1.record()
+        barrier()
+        nozero_ms = e0.elapsed_time(e1) / k_nz
 
     # ---- the two phases apart (three-launch form), outside the timed region ------------------
     split_ms = None
@@ -786,6 +825,10 @@ def run_ours(args):
                                  "(a second read of the gradients) and the update pass; a caller whose "
                                  "gradient producer supplies the sum of squares pays the update pass only")
         line["phases_ms"]["update_only_roofline_frac"] = alg_bytes * n / (split_ms["update"] * 1e-3) / 1e9 / peak
+        line["without_zero_grad"] = {"ms_per_step": nozero_ms,
+                                     "roofline_frac": alg_bytes * n / (nozero_ms * 1e-3) / 1e9 / peak,
+                                     "note": "side measurement, not the contract's step: ANNI_STEP_ZERO_GRAD off "
+                                             "(22 instead of 24 bytes per parameter issued)"}
         base, _ = cpu_reference_step_rate(64 * 1024 * 1024, 3, 1)
         line["cpu_baseline"] = base
     print(json.dumps(line), flush=True)
@@ -801,6 +844,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--profile", action="store_true",
+                    help="warm-up and timed steps only (no side measurements): the command profiler captures run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

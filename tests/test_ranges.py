@@ -175,3 +175,33 @@ def test_fp8_step_in_one_launch_equals_the_other_forms(monkeypatch):
     for other in outs[1:]:
         for a, b in zip(outs[0], other):
             assert np.array_equal(a, b)
+
+
+def test_rotated_peer_order_on_local_arenas():
+    """anni_optstep_rotate_peers with three "ranks" standing on one GPU (their arenas are local
+    buffers): whatever peer comes first, the reduced gradients (an exact sum here), the sum of
+    squares and the twins stored into every arena are the same; a bad start index is refused."""
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    p, g, m, v = make_inputs(n, seed=5, grad_dtype=DT_BF16, state_dtype=DT_F32)
+    hp = OptStep.hyper(lr=3e-4, t=2, beta2=0.95, wd=0.1, clip=1.0)
+    base = to_dev(g).float()
+    parts = [(base * w).to(torch.bfloat16) for w in (0.5, 0.25, 0.25)]      # sums exactly to g
+    outs = []
+    for first in (0, 1, 2):
+        eng = _engine(segs, DT_BF16, DT_F32, p, g, m, v)
+        eng.grad.zero_()
+        twins = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+        eng.set_peers([x.data_ptr() for x in parts], [t.data_ptr() for t in twins], None, 0)
+        eng.rotate_peers(first)
+        eng.reduce_norm(hp)
+        eng.update(hp)
+        st = eng.status()
+        assert st.error == 0 and st.skipped == 0
+        assert all(torch.equal(t, twins[0]) for t in twins) and bool(twins[0].any())
+        outs.append((st.norm, to_host(eng.master).copy(), to_host(twins[2]).copy()))
+        with pytest.raises(AnniError):
+            eng.rotate_peers(3)
+        eng.close()
+    for o in outs[1:]:
+        assert o[0] == outs[0][0] and np.array_equal(o[1], outs[0][1]) and np.array_equal(o[2], outs[0][2])
