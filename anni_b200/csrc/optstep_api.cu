@@ -213,8 +213,8 @@ extern "C" int anni_optstep_create(const anni_optstep_config *cfg, anni_optstep 
 		/*
 		** ANNI_B200_FP8_PIPE=1: quantise tensor by tensor behind the update instead of in a phase of
 		** its own after a second grid barrier.  Off by default: it takes the quantiser's reads off
-		** HBM (they hit the L2) but not off the path between the SMs and the L2, which is what
-		** bounds the step, and its bookkeeping costs 6 % (555 M parameters: 2.58 against 2.42 ms).
+		** HBM (91 % of them hit the L2) but not off the path between the SMs and the L2, and its
+		** bookkeeping costs more than the DRAM time it saves (555 M parameters: 2.58 against 2.42 ms).
 		*/
 		const char *e = getenv("ANNI_B200_FP8_PIPE");
 
