@@ -191,3 +191,29 @@ def test_zero1_driver_geometry_and_argument_checks():
     assert L.anni_zero1_unique_id(None) == E_ARG
     assert L.anni_zero1_comm_init(None, 0, 2, C.byref(h)) == E_ARG
     assert L.anni_zero1_nccl_available() in (0, 1)
+
+
+def test_shard_geometry_properties():
+    """Shard geometry of the C driver over many arena sizes and world sizes: shards are whole
+    multiples of 4096 elements, cover the arena exactly once in rank order, and agree with the
+    Python driver's."""
+    from hypothesis import given, settings, strategies as st
+    from anni_b200.zero1 import shard_geometry
+    L = capi.lib()
+    u64 = C.c_uint64
+
+    @settings(max_examples=200, deadline=None)
+    @given(n=st.integers(min_value=1, max_value=3_000_000_000), world=st.integers(min_value=1, max_value=8))
+    def check(n, world):
+        per, own = shard_geometry(n, world)
+        covered = 0
+        for rank in range(world):
+            a, b, c = u64(), u64(), u64()
+            assert L.anni_zero1_geometry(n, world, rank, C.byref(a), C.byref(b), C.byref(c)) == capi.OK
+            assert a.value == per and a.value % 4096 == 0 and a.value * world >= n
+            assert c.value == own[rank][1] and c.value <= a.value
+            if c.value:
+                assert b.value == covered == rank * a.value
+            covered += c.value
+        assert covered == n
+    check()
