@@ -11,6 +11,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <thread>
 #include "anni_gpu_compat.h"
 #include "anni_lm_adam.h"
 #include "optstep_internal.h"
@@ -553,6 +554,33 @@ extern "C" int anni_lm_adam_sync_host(anni_lm_adam *opt)
 
 /* ---- the step ----------------------------------------------------------------------- */
 
+/*
+** Clears the host gradient arrays.  With a model's worth of them (hundreds of megabytes when
+** every gradient lives on the host) one core needs tens of milliseconds, so the tensors are
+** dealt out to a few threads; small totals are cleared in place.
+*/
+static void host_zero_grads(anni_lm_adam *opt)
+{
+	int64_t total = 0;
+	int parts;
+	std::thread th[3];
+
+	for (int i = 0; i < opt->n_segs; i++)
+		if (opt->segs[i].dw)
+			total += opt->segs[i].n;
+	parts = total >= ((int64_t)32 << 20) ? 4 : 1;
+	auto work = [opt, parts](int k) {
+		for (int i = k; i < opt->n_segs; i += parts)
+			if (opt->segs[i].dw)
+				memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
+	};
+	for (int k = 1; k < parts; k++)
+		th[k - 1] = std::thread(work, k);
+	work(0);
+	for (int k = 1; k < parts; k++)
+		th[k - 1].join();
+}
+
 /* ANN_GNORM_EVERY=k: report the gradient norm every k-th step (adam_gnorm_every, lm_adam.c:438-450) */
 static int gnorm_every(void)
 {
@@ -614,6 +642,8 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	rc = anni_optstep_step(opt->engine, &hp, NULL);
 	if (rc != ANNI_OK)
 		goto fail;
+	if (host_grads)			/* seg_scatter zeroes the host gradient vectors (lm_adam.c:413); the */
+		host_zero_grads(opt);	/* uploads are complete, so this runs beside the device step */
 	rc = anni_optstep_status_read(opt->engine, &st, NULL);
 	if (rc == ANNI_OK && st.error != 0)
 		rc = st.error;
@@ -630,10 +660,6 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 			fprintf(stderr, "[adam] step %d grad norm %.4g%s\n", opt->t, st.norm,
 			    opt->grad_clip > 0.0 && st.norm > opt->grad_clip ? " (clipped)" : "");
 	}
-	if (host_grads)			/* seg_scatter zeroes the host gradient vectors (lm_adam.c:413) */
-		for (i = 0; i < opt->n_segs; i++)
-			if (opt->segs[i].dw)
-				memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
 	opt->params_valid = 1;
 	gpu_half_wt_invalidate(NULL);	/* lm_adam.c:547: derived copies rebuild */
 	if (opt->offload_mv) {		/* adam_offload_mv (lm_adam.c:314-334) */
