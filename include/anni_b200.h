@@ -351,6 +351,13 @@ int	anni_optstep_status_noalloc(anni_optstep_status *out, void *stream);
 */
 int	anni_optstep_selftest_barrier_timeout(anni_optstep *h, unsigned max_polls, void *stream);
 
+/*
+** Diagnostics of the optional one-launch e4m3 form (ANNI_B200_FP8_PIPE=1): polls its blocks have
+** spent waiting for each other's tensors since the last call (waits for `stream`, reads and
+** clears the counter; -1 on error).  No counterpart in the reference.
+*/
+long long anni_optstep_pipe_polls(anni_optstep *h, void *stream);
+
 /* Launch geometry in use (blocks of the persistent grid, threads per block). */
 int	anni_optstep_grid(anni_optstep *h, int *blocks, int *threads);
 
