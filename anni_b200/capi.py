@@ -13,6 +13,7 @@ _LIB = None
 DT_F32, DT_BF16 = 0, 1
 SEG_WD, SEG_TWIN_BF16, SEG_TWIN_FP8 = 1, 2, 4
 STEP_CHECK_FINITE, STEP_ZERO_GRAD, STEP_DEV_LOSS_SCALE, STEP_EXACT_UPDATE = 1, 2, 4, 8
+STEP_REDUCE_CLEARS_OWN = 16     # peer-memory ZeRO-1: the reduce clears this rank's own arena part
 OK, E_ARG, E_CUDA, E_BARRIER_TIMEOUT, E_NOMEM, E_LIMIT = 0, -1, -2, -3, -4, -5
 NOALLOC_MAX_SEG = 1024
 RANGE_ACCUMULATE, RANGE_LAST, RANGE_LOCAL_TWINS, RANGE_FIRST = 1, 2, 4, 8

@@ -11,6 +11,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <atomic>
 #include <thread>
 #include "anni_gpu_compat.h"
 #include "anni_lm_adam.h"
@@ -555,31 +556,81 @@ extern "C" int anni_lm_adam_sync_host(anni_lm_adam *opt)
 /* ---- the step ----------------------------------------------------------------------- */
 
 /*
-** Clears the host gradient arrays.  With a model's worth of them (hundreds of megabytes when
-** every gradient lives on the host) one core needs tens of milliseconds, so the tensors are
-** dealt out to a few threads; small totals are cleared in place.
+** Clears the host gradient arrays (seg_scatter, lm_adam.c:413 of the reference).  With a
+** model's worth of them (hundreds of megabytes when every gradient lives on the host) one core
+** needs tens of milliseconds, so the tensors are dealt out to a few threads, and a tensor is
+** cleared as soon as ITS upload has returned, beside the uploads of the later ones: the step
+** then costs the longer of the two instead of their sum.  Small totals are cleared in place
+** after the launch.
 */
-static void host_zero_grads(anni_lm_adam *opt)
-{
-	int64_t total = 0;
-	int parts;
-	std::thread th[3];
+struct grad_clearer {
+	anni_lm_adam		*opt = nullptr;
+	std::atomic<int>	ready{0};	/* tensors [0, ready) have been uploaded */
+	std::atomic<int>	stop{0};
+	std::thread		th[8];
+	int			n_th = 0;
 
-	for (int i = 0; i < opt->n_segs; i++)
-		if (opt->segs[i].dw)
-			total += opt->segs[i].n;
-	parts = total >= ((int64_t)32 << 20) ? 4 : 1;
-	auto work = [opt, parts](int k) {
-		for (int i = k; i < opt->n_segs; i += parts)
-			if (opt->segs[i].dw)
-				memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
-	};
-	for (int k = 1; k < parts; k++)
-		th[k - 1] = std::thread(work, k);
-	work(0);
-	for (int k = 1; k < parts; k++)
-		th[k - 1].join();
-}
+	static int64_t host_elems(const anni_lm_adam *o)
+	{
+		int64_t total = 0;
+
+		for (int i = 0; i < o->n_segs; i++)
+			if (o->segs[i].dw)
+				total += o->segs[i].n;
+		return total;
+	}
+	void start(anni_lm_adam *o)
+	{
+		const unsigned hw = std::thread::hardware_concurrency();
+
+		opt = o;
+		if (host_elems(o) < ((int64_t)32 << 20))
+			return;			/* cleared by clear_now() after the launch */
+		n_th = hw >= 16 ? 8 : hw >= 8 ? 4 : 2;
+		for (int k = 0; k < n_th; k++)
+			th[k] = std::thread([this, k]() {
+				for (int i = k; i < opt->n_segs; i += n_th) {
+					if (!opt->segs[i].dw)
+						continue;
+					while (ready.load(std::memory_order_acquire) <= i) {
+						if (stop.load(std::memory_order_relaxed))
+							return;
+						std::this_thread::yield();
+					}
+					memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
+				}
+			});
+	}
+	void uploaded(int i)
+	{
+		ready.store(i + 1, std::memory_order_release);
+	}
+	/* after the launch: waits for the threads, or clears small totals here */
+	void finish()
+	{
+		if (!opt)
+			return;
+		if (n_th == 0) {
+			for (int i = 0; i < opt->n_segs; i++)
+				if (opt->segs[i].dw)
+					memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
+		}
+		join();
+		opt = nullptr;
+	}
+	void join()
+	{
+		for (int k = 0; k < n_th; k++)
+			if (th[k].joinable())
+				th[k].join();
+		n_th = 0;
+	}
+	~grad_clearer()		/* a step that failed on the way: what was not uploaded stays as it is */
+	{
+		stop.store(1, std::memory_order_relaxed);
+		join();
+	}
+};
 
 /* ANN_GNORM_EVERY=k: report the gradient norm every k-th step (adam_gnorm_every, lm_adam.c:438-450) */
 static int gnorm_every(void)
@@ -605,6 +656,7 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 {
 	anni_optstep_hyper hp;
 	anni_optstep_status st;
+	grad_clearer clearer;
 	int host_grads = 0;
 	int rc;
 	int i;
@@ -620,9 +672,21 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 		if (opt->segs[i].dw)
 			host_grads = 1;
 	if (host_grads) {		/* seg_gather (lm_adam.c:361-396) for host-resident gradients */
-		rc = anni_lm_adam_upload_grads(opt);
-		if (rc != ANNI_OK)
+		if (!opt->d_grad) {
+			rc = ANNI_E_ARG;
 			goto fail;
+		}
+		clearer.start(opt);
+		for (i = 0; i < opt->n_segs; i++) {
+			const anni_lm_adam_seg *s = &opt->segs[i];
+
+			if (s->dw && upload_as((char *)opt->d_grad + (size_t)s->off * elem_size(opt->grad_dtype),
+			    opt->grad_dtype, s->dw, s->n) != 0) {
+				rc = ANNI_E_CUDA;
+				goto fail;
+			}
+			clearer.uploaded(i);	/* the copy has returned: the source may change */
+		}
 	}
 	memset(&hp, 0, sizeof(hp));
 	hp.lr = lr;
@@ -642,8 +706,7 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	rc = anni_optstep_step(opt->engine, &hp, NULL);
 	if (rc != ANNI_OK)
 		goto fail;
-	if (host_grads)			/* seg_scatter zeroes the host gradient vectors (lm_adam.c:413); the */
-		host_zero_grads(opt);	/* uploads are complete, so this runs beside the device step */
+	clearer.finish();		/* the host gradient vectors are zero from here on (lm_adam.c:413) */
 	rc = anni_optstep_status_read(opt->engine, &st, NULL);
 	if (rc == ANNI_OK && st.error != 0)
 		rc = st.error;

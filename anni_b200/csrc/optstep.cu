@@ -590,28 +590,39 @@ __device__ __forceinline__ void adam_elem(const anni_launch &a, double coef, flo
 	p = __fmaf_rn(-lrwd, p, p);
 }
 
+/*
+** How a kernel variant treats what follows the plain update: MODE_PLAIN clears the bound
+** gradient buffer; MODE_PIPE (one-launch step only) also quantises e4m3 twins behind the
+** update; MODE_ARENA (update kernel only) clears every part of the rank's full gradient arena
+** instead of the bound buffer.  Compile-time, so that the plain variants carry none of the
+** other two's registers.
+*/
+enum { MODE_PLAIN = 0, MODE_PIPE = 1, MODE_ARENA = 2 };
+
 /* "the step leaves the gradients zeroed": the bound buffer, or every part of the rank's full arena */
-template <typename GradT>
+template <typename GradT, int MODE>
 __device__ __forceinline__ void zero_grad4(const anni_launch &a, uint64_t e)
 {
-	if (a.zero_parts > 0) {
+	if (MODE == MODE_ARENA) {
 		for (int k = 0; k < a.zero_parts; k++)
-			io4<GradT>::zero(a.zero_base, (uint64_t)k * a.zero_stride + e);
+			if (k + 1 != a.zero_done)
+				io4<GradT>::zero(a.zero_base, (uint64_t)k * a.zero_stride + e);
 	} else
 		io4<GradT>::zero(a.grad, e);
 }
 
-template <typename GradT>
+template <typename GradT, int MODE>
 __device__ __forceinline__ void zero_grad1(const anni_launch &a, uint64_t i)
 {
-	if (a.zero_parts > 0) {
+	if (MODE == MODE_ARENA) {
 		for (int k = 0; k < a.zero_parts; k++)
-			io8<GradT>::store1(a.zero_base, (uint64_t)k * a.zero_stride + i, 0.0f);
+			if (k + 1 != a.zero_done)
+				io8<GradT>::store1(a.zero_base, (uint64_t)k * a.zero_stride + i, 0.0f);
 	} else
 		io8<GradT>::store1(a.grad, i, 0.0f);
 }
 
-template <typename GradT, typename StateT, bool EXACT, bool PIPE = false>
+template <typename GradT, typename StateT, bool EXACT, int MODE>
 __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t e, double coef,
 	uint32_t sflags, float &tmax, uint64_t seg_base, int64_t pack_off, uint32_t pack_ld,
 	uint32_t pack_cols)
@@ -625,7 +636,7 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 #pragma unroll
 	for (int k = 0; k < ANNI_UVEC; k++)
 		adam_elem<EXACT>(a, coef, lrwd, g.x[k], p.x[k], m.x[k], v.x[k]);
-	if (PIPE && (sflags & ANNI_SEG_TWIN_FP8) && !(a.flags & ANNI_LAUNCH_PIPE_STREAM))
+	if (MODE == MODE_PIPE && (sflags & ANNI_SEG_TWIN_FP8) && !(a.flags & ANNI_LAUNCH_PIPE_STREAM))
 		io4<float>::store_keep(a.master, e, p);	/* read back for its e4m3 code while still in L2 */
 	else
 		io4<float>::store(a.master, e, p);
@@ -657,11 +668,11 @@ __device__ __forceinline__ void update_chunk_vec(const anni_launch &a, uint64_t 
 		    + (ws - r * pack_cols), p);
 	}
 	if (a.flags & ANNI_STEP_ZERO_GRAD)
-		zero_grad4<GradT>(a, e);
+		zero_grad4<GradT, MODE>(a, e);
 }
 
 /* element-wise path for chunks that cross a tensor boundary, the arena end, or unaligned buffers */
-template <typename GradT, typename StateT, bool EXACT>
+template <typename GradT, typename StateT, bool EXACT, int MODE>
 __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64_t e, double coef,
 	bool skip)
 {
@@ -702,7 +713,7 @@ __device__ __forceinline__ void update_chunk_scalar(const anni_launch &a, uint64
 			}
 		}
 		if (a.flags & ANNI_STEP_ZERO_GRAD)
-			zero_grad1<GradT>(a, i);
+			zero_grad1<GradT, MODE>(a, i);
 	}
 }
 
@@ -719,7 +730,7 @@ __device__ __forceinline__ void amax_flush(const anni_launch &a, int seg, float 
 }
 
 /* one chunk the general way: tensor looked up from scratch, element-wise when the chunk is not whole */
-template <typename GradT, typename StateT, bool EXACT, bool PIPE>
+template <typename GradT, typename StateT, bool EXACT, int MODE>
 __device__ __forceinline__ void update_chunk_general(const anni_launch &a, const decision &d, uint64_t base,
 	uint64_t t4, float &tmax, int &amax_seg)
 {
@@ -739,15 +750,15 @@ __device__ __forceinline__ void update_chunk_general(const anni_launch &a, const
 		if (a.seg_aux) {
 			const anni_seg_derived ax = a.seg_aux[seg];
 
-			update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base + t4, d.coef, sflags, tmax,
+			update_chunk_vec<GradT, StateT, EXACT, MODE>(a, base + t4, d.coef, sflags, tmax,
 			    (uint64_t)a.seg_off[seg] - a.arena_off, ax.pack_off, (uint32_t)ax.pack_ld,
 			    (uint32_t)ax.cols);
 		} else
-			update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base + t4, d.coef, sflags, tmax, 0, 0, 0, 1);
+			update_chunk_vec<GradT, StateT, EXACT, MODE>(a, base + t4, d.coef, sflags, tmax, 0, 0, 0, 1);
 	} else if (whole) {
-		zero_grad4<GradT>(a, base + t4);	/* skipped step: only the gradients change */
+		zero_grad4<GradT, MODE>(a, base + t4);	/* skipped step: only the gradients change */
 	} else
-		update_chunk_scalar<GradT, StateT, EXACT>(a, base + t4, d.coef, d.skip);
+		update_chunk_scalar<GradT, StateT, EXACT, MODE>(a, base + t4, d.coef, d.skip);
 }
 
 /* dequantisation scale of a tensor from its amax (num/gpu_cuda.cu:927-938 of the reference) */
@@ -969,7 +980,7 @@ __device__ __forceinline__ bool pipe_work(const anni_launch &a, pipe_state &q, i
 ** few hundred of them -- takes the short road: tensor flags looked up once, then nothing
 ** but loads, arithmetic and stores per chunk.  The others go chunk by chunk the general way.
 */
-template <typename GradT, typename StateT, bool EXACT, bool PIPE>
+template <typename GradT, typename StateT, bool EXACT, int MODE>
 __device__ __forceinline__ bool update_phase(const anni_launch &a, const decision &d)
 {
 	const chunk_walk w = walk_init(a.n, a.sc_log2, ANNI_UCHUNK_LOG2);
@@ -998,7 +1009,7 @@ __device__ __forceinline__ bool update_phase(const anni_launch &a, const decisio
 
 		if (c0 >= w.chunks)
 			continue;
-		if (PIPE && !d.skip) {
+		if (MODE == MODE_PIPE && !d.skip) {
 			const int64_t top = alo + (int64_t)span;	/* this and all later super-chunks lie below */
 
 			while (rep_hi >= 0 && a.seg_off[rep_hi] >= top) {
@@ -1031,25 +1042,25 @@ __device__ __forceinline__ bool update_phase(const anni_launch &a, const decisio
 
 #pragma unroll 1
 				for (uint32_t k = per; k > 0; k--)
-					update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
+					update_chunk_vec<GradT, StateT, EXACT, MODE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
 					    d.coef, sflags, tmax, seg_base, ax.pack_off, (uint32_t)ax.pack_ld,
 					    (uint32_t)ax.cols);
 			} else {
 #pragma unroll 1
 				for (uint32_t k = per; k > 0; k--)
-					update_chunk_vec<GradT, StateT, EXACT, PIPE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
+					update_chunk_vec<GradT, StateT, EXACT, MODE>(a, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK + t4,
 					    d.coef, sflags, tmax, 0, 0, 0, 1);
 			}
 		} else {
 			for (uint32_t k = per; k > 0; k--)
 				if (c0 + (k - 1) < w.chunks)
-					update_chunk_general<GradT, StateT, EXACT, PIPE>(a, d, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK,
+					update_chunk_general<GradT, StateT, EXACT, MODE>(a, d, base0 + (uint64_t)(k - 1) * ANNI_UCHUNK,
 					    t4, tmax, amax_seg);
 		}
 	}
 	if (amax_seg >= 0)
 		amax_flush(a, amax_seg, tmax);
-	if (PIPE && !d.skip) {
+	if (MODE == MODE_PIPE && !d.skip) {
 		/* the walk is over: report what is left, then quantise what is left */
 		while (rep_hi >= 0)
 			pipe_report(a, rep_hi--);
@@ -1236,6 +1247,10 @@ template <> struct raw8<__nv_bfloat16> {
 	{
 		q = mc_ld_reduce_bf16x8(static_cast<const uint16_t *>(mc) + e);
 	}
+	static __device__ __forceinline__ void clear(void *base, uint64_t e)
+	{
+		__stcs(reinterpret_cast<uint4 *>(static_cast<uint16_t *>(base) + e), make_uint4(0, 0, 0, 0));
+	}
 	__device__ __forceinline__ f32x8 widen() const
 	{
 		return unpack_bf16x8(q);
@@ -1255,6 +1270,13 @@ template <> struct raw8<float> {
 	{
 		q[0] = mc_ld_reduce_f32x4(static_cast<const float *>(mc) + e);
 		q[1] = mc_ld_reduce_f32x4(static_cast<const float *>(mc) + e + 4);
+	}
+	static __device__ __forceinline__ void clear(void *base, uint64_t e)
+	{
+		uint4 *p = reinterpret_cast<uint4 *>(static_cast<float *>(base) + e);
+
+		__stcs(p, make_uint4(0, 0, 0, 0));
+		__stcs(p + 1, make_uint4(0, 0, 0, 0));
 	}
 	__device__ __forceinline__ f32x8 widen() const
 	{
@@ -1291,6 +1313,9 @@ __device__ __forceinline__ void reduce_store(const anni_launch &a, const raw8<Gr
 	if (sizeof(GradT) == 2)		/* what the update will read back: the rounded value */
 		sum = unpack_bf16x8(pack_bf16x8(sum));
 	io8<GradT>::store(a.grad, e, sum);
+	if (a.own_clear) {		/* this thread's own load of these elements has been consumed above */
+		raw8<GradT>::clear(a.own_clear, e);
+	}
 	norm_accumulate<GradT>(sum, acc0, acc1);
 }
 
@@ -1385,6 +1410,8 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) reduce_norm_kernel(const anni
 				for (int k = 1; k < np; k++)
 					x = __fadd_rn(x, io8<GradT>::load1(a.peer_grad[k], e + j));
 				io8<GradT>::store1(a.grad, e + j, x);
+				if (a.own_clear)
+					io8<GradT>::store1(a.own_clear, e + j, 0.0f);
 				x = io8<GradT>::load1(a.grad, e + j);
 				acc0 = fma((double)x, (double)x, acc0);
 			}
@@ -1412,7 +1439,7 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) reduce_norm_kernel(const anni
 }
 
 /* Update only (second launch of the split sequence, or the legacy call with a host multiplier). */
-template <typename GradT, typename StateT, bool EXACT>
+template <typename GradT, typename StateT, bool EXACT, bool ARENA>
 __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_launch a)
 {
 	decision d;
@@ -1429,7 +1456,7 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) update_kernel(const anni_laun
 			a.ctl->skipped = d.skip ? 1 : 0;
 		}
 	}
-	update_phase<GradT, StateT, EXACT, false>(a, d);
+	update_phase<GradT, StateT, EXACT, ARENA ? MODE_ARENA : MODE_PLAIN>(a, d);
 	if (!(a.flags & ANNI_LAUNCH_NO_EPILOGUE))
 		step_epilogue(a.ctl, d.skip);
 }
@@ -1473,7 +1500,7 @@ __global__ void __launch_bounds__(ANNI_THREADS, 4) fused_kernel(const anni_launc
 		a.ctl->eff_scale = d.coef;
 		a.ctl->skipped = d.skip ? 1 : 0;
 	}
-	if (!update_phase<GradT, StateT, EXACT, PIPE>(a, d))
+	if (!update_phase<GradT, StateT, EXACT, PIPE ? MODE_PIPE : MODE_PLAIN>(a, d))
 		return;
 	if (!PIPE && (a.flags & ANNI_LAUNCH_HAS_FP8) && !d.skip) {
 		if (!grid_barrier(a.ctl, ++barriers * gridDim.x))
@@ -1689,10 +1716,17 @@ template <typename K> int occupancy_blocks(K kernel)
 template <typename GradT, typename StateT>
 int launch_update_t(const anni_launch *a, int blocks, cudaStream_t st)
 {
-	if (a->flags & ANNI_STEP_EXACT_UPDATE)
-		update_kernel<GradT, StateT, true><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	const bool arena = a->zero_parts > 0;	/* a full gradient arena to clear instead of the bound buffer */
+
+	if (a->flags & ANNI_STEP_EXACT_UPDATE) {
+		if (arena)
+			update_kernel<GradT, StateT, true, true><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+		else
+			update_kernel<GradT, StateT, true, false><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+	} else if (arena)
+		update_kernel<GradT, StateT, false, true><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	else
-		update_kernel<GradT, StateT, false><<<blocks, ANNI_THREADS, 0, st>>>(*a);
+		update_kernel<GradT, StateT, false, false><<<blocks, ANNI_THREADS, 0, st>>>(*a);
 	return cudaGetLastError() == cudaSuccess ? ANNI_OK : ANNI_E_CUDA;
 }
 
@@ -1715,10 +1749,10 @@ int launch_fused_t(const anni_launch *a, int blocks, cudaStream_t st)
 template <typename GradT, typename StateT> int grid_t(int cooperative)
 {
 	int best = cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true, false>)
-	    : occupancy_blocks(update_kernel<GradT, StateT, true>);
+	    : occupancy_blocks(update_kernel<GradT, StateT, true, true>);
 	const int others[3] = {
 		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false, false>)
-		    : occupancy_blocks(update_kernel<GradT, StateT, false>),
+		    : occupancy_blocks(update_kernel<GradT, StateT, false, true>),
 		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, true, true>) : best,
 		cooperative ? occupancy_blocks(fused_kernel<GradT, StateT, false, true>) : best,
 	};

@@ -51,6 +51,59 @@ static void use_grad_arena(const anni_optstep *h, anni_launch *la)
 	}
 }
 
+/*
+** Which part of the named arena is this rank's own, i.e. which peer pointer lies inside it at a
+** part boundary: the part's index, or -1.  *slot = that peer's position in the table.
+*/
+static int own_part(const anni_optstep *h, int *slot)
+{
+	const size_t gsz = h->cfg.grad_dtype == ANNI_DT_BF16 ? 2u : 4u;
+	const uintptr_t base = (uintptr_t)h->grad_arena;
+	const uintptr_t part = (uintptr_t)h->grad_arena_stride * gsz;
+
+	if (!h->grad_arena || part == 0)
+		return -1;
+	for (int k = 0; k < h->la.n_peers; k++) {
+		const uintptr_t p = (uintptr_t)h->la.peer_grad[k];
+
+		if (p >= base && p < base + part * (uintptr_t)h->grad_arena_parts && (p - base) % part == 0) {
+			if (slot)
+				*slot = k;
+			return (int)((p - base) / part);
+		}
+	}
+	return -1;
+}
+
+/* ANNI_STEP_REDUCE_CLEARS_OWN on the reduce side: name the part to clear, or refuse */
+static int reduce_clears_own(const anni_optstep *h, anni_launch *la)
+{
+	int slot = 0;
+
+	la->own_clear = NULL;
+	if (!(la->flags & ANNI_STEP_REDUCE_CLEARS_OWN))
+		return ANNI_OK;
+	if (!(la->flags & ANNI_STEP_ZERO_GRAD) || la->mc_grad || own_part(h, &slot) < 0)
+		return ANNI_E_ARG;
+	la->own_clear = const_cast<void *>(la->peer_grad[slot]);
+	return ANNI_OK;
+}
+
+/* ... and on the update side: that part is done */
+static int update_skips_own(const anni_optstep *h, anni_launch *la)
+{
+	int part;
+
+	la->zero_done = 0;
+	if (!(la->flags & ANNI_STEP_REDUCE_CLEARS_OWN))
+		return ANNI_OK;
+	part = own_part(h, NULL);
+	if (!(la->flags & ANNI_STEP_ZERO_GRAD) || la->zero_parts < 1 || part < 0)
+		return ANNI_E_ARG;
+	la->zero_done = part + 1;
+	return ANNI_OK;
+}
+
 /* ... and what lies beyond this shard's length in every part, which the update's walk never visits */
 static int zero_arena_tail(const anni_optstep *h, const anni_launch *la, cudaStream_t st)
 {
@@ -333,6 +386,9 @@ extern "C" int anni_optstep_update(anni_optstep *h, const anni_optstep_hyper *hp
 	    != cudaSuccess)
 		return ANNI_E_CUDA;
 	use_grad_arena(h, &la);
+	rc = update_skips_own(h, &la);
+	if (rc != ANNI_OK)
+		return rc;
 	{
 		const int slot = anni_op_begin(ANNI_OP_ADAM, st);
 
@@ -541,6 +597,9 @@ extern "C" int anni_optstep_reduce_norm(anni_optstep *h, const anni_optstep_hype
 		return rc;
 	if (la.n_peers < 1)
 		return ANNI_E_ARG;
+	rc = reduce_clears_own(h, &la);
+	if (rc != ANNI_OK)
+		return rc;
 	return anni_launch_reduce_norm(&la, h->cfg.grad_dtype, h->blocks_rn, (cudaStream_t)stream);
 }
 
@@ -571,6 +630,8 @@ static int restrict_range(const anni_optstep *h, anni_launch *la, uint64_t off, 
 	}
 	if (la->zero_base)
 		la->zero_base = (char *)la->zero_base + off * gsz;
+	if (la->own_clear)
+		la->own_clear = (char *)la->own_clear + off * gsz;
 	if (la->mc_grad)
 		la->mc_grad = (const char *)la->mc_grad + off * gsz;
 	if (la->mc_twin)
@@ -590,6 +651,9 @@ extern "C" int anni_optstep_reduce_norm_range(anni_optstep *h, const anni_optste
 		return rc;
 	if (la.n_peers < 1)
 		return ANNI_E_ARG;
+	rc = reduce_clears_own(h, &la);
+	if (rc != ANNI_OK)
+		return rc;
 	rc = restrict_range(h, &la, elem_off, elem_n);
 	if (rc != ANNI_OK)
 		return rc;
@@ -610,6 +674,9 @@ extern "C" int anni_optstep_update_range(anni_optstep *h, const anni_optstep_hyp
 	if (la.seg_aux)
 		return ANNI_E_ARG;	/* derived twins are a whole-arena, one-GPU feature */
 	use_grad_arena(h, &la);
+	rc = update_skips_own(h, &la);
+	if (rc != ANNI_OK)
+		return rc;
 	rc = restrict_range(h, &la, elem_off, elem_n);
 	if (rc != ANNI_OK)
 		return rc;

@@ -130,6 +130,14 @@ typedef struct anni_launch {
 	void		*zero_base;
 	uint64_t	zero_stride;
 	int		zero_parts;
+	/*
+	** Peer-memory ZeRO-1: this rank's own part of its arena is read by nobody else, so the
+	** reduce can clear it as it reads it, while the links rather than local memory bound that
+	** kernel.  own_clear = that part at shard element 0 (reduce: clear what was read; NULL: leave
+	** it), zero_done = 1 + the index of a part the update need not clear any more (0: none).
+	*/
+	void		*own_clear;
+	int		zero_done;
 	anni_control	*ctl;
 } anni_launch;
 

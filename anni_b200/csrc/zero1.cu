@@ -92,6 +92,8 @@ struct anni_zero1 {
 	const void	*mc_grad;
 	void		*mc_twin;
 	void		*mc_twin8;
+	int		mc_on;		/* the reduce and the twin stores go through the multicast addresses */
+	int		clear_own;	/* the reduce clears this rank's own part of the arena (knob) */
 	float		*d_tick;	/* one float: the ordering exchanges */
 	int		bound;
 };
@@ -172,9 +174,12 @@ static int attach(anni_zero1 *z, const void *const *peer_grad, const void *mc_gr
 	if (rc != ANNI_OK)
 		return rc;
 	z->mc_grad = mc_grad;
-	if (mc_grad && z->mc_twin && (!z->has_fp8 || z->mc_twin8))
+	z->mc_on = 0;
+	if (mc_grad && z->mc_twin && (!z->has_fp8 || z->mc_twin8)) {
 		rc = anni_optstep_set_multicast(z->eng, mc_grad, z->mc_twin, z->mc_twin8,
 		    (uint64_t)z->rank * z->per);
+		z->mc_on = rc == ANNI_OK;
+	}
 	return rc;
 }
 
@@ -230,6 +235,11 @@ extern "C" int anni_zero1_create(const anni_zero1_config *cfg, anni_zero1 **out)
 	z->twin_fp8_arena = cfg->twin_fp8_arena;
 	z->mc_twin = cfg->mc_twin;
 	z->mc_twin8 = cfg->mc_twin_fp8;
+	{
+		const char *e = getenv("ANNI_B200_REDUCE_CLEARS_OWN");	/* 0: the update clears every part (tuning) */
+
+		z->clear_own = !(e && atoi(e) == 0);
+	}
 	(void)anni_zero1_geometry(cfg->n_arena, cfg->world, cfg->rank, &z->per, &z->shard_off, &z->shard_n);
 	memset(&ec, 0, sizeof(ec));
 	ec.n_arena = cfg->n_arena;
@@ -342,6 +352,7 @@ extern "C" int anni_zero1_step(anni_zero1 *z, const anni_optstep_hyper *hp, int 
 	cudaStream_t st = (cudaStream_t)stream;
 	const nccl_api *n;
 	const int gtype = z && z->grad_dtype == ANNI_DT_BF16 ? NCCL_BFLOAT16 : NCCL_FLOAT32;
+	anni_optstep_hyper own;
 	int rc;
 
 	if (!z || !hp || !z->bound)
@@ -358,6 +369,12 @@ extern "C" int anni_zero1_step(anni_zero1 *z, const anni_optstep_hyper *hp, int 
 	if (z->peer) {
 		if (!(flags & ANNI_ZERO1_GRADS_COMPLETE))
 			TRY(tick(z, st));
+		/* nobody else reads this rank's own part of its arena: cleared while the links are the bound */
+		if (z->clear_own && !z->mc_on && (hp->flags & ANNI_STEP_ZERO_GRAD)) {
+			own = *hp;
+			own.flags |= ANNI_STEP_REDUCE_CLEARS_OWN;
+			hp = &own;
+		}
 		TRY(anni_optstep_reduce_norm(z->eng, hp, stream));
 	} else {
 		if (n->reduce_scatter(z->grad_arena, z->grad_shard, (size_t)z->per, gtype, NCCL_SUM, z->comm, st) != 0)

@@ -64,7 +64,7 @@ import os
 import torch
 import torch.distributed as dist
 
-from .capi import DT_BF16, DT_F32
+from .capi import DT_BF16, DT_F32, STEP_REDUCE_CLEARS_OWN, STEP_ZERO_GRAD
 
 _TORCH_DT = {DT_F32: torch.float32, DT_BF16: torch.bfloat16}
 SHARD_ALIGN = 4096      # elements: keeps every shard base 16-byte aligned for all dtypes
@@ -469,6 +469,12 @@ class Zero1:
         if self.peer:
             if not grads_complete:
                 self._barrier()
+            if (not self.uses_multicast and self._arena_by_engine and (hp.flags & STEP_ZERO_GRAD)
+                    and os.environ.get("ANNI_B200_REDUCE_CLEARS_OWN", "1") != "0"):
+                # nobody else reads this rank's own part of its arena: the reduce clears it
+                own = type(hp).from_buffer_copy(hp)
+                own.flags |= STEP_REDUCE_CLEARS_OWN
+                hp = own
             self.eng.reduce_norm(hp)
             mark("reduce_scatter+norm")
             dist.all_reduce(self.eng.reduce_tensor(), op=dist.ReduceOp.SUM, group=self.group)

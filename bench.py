@@ -770,20 +770,24 @@ def run_ours(args):
         opt = lm_adam.create(segs1, hw.data_ptr(), hg.data_ptr())
         o = opt.contents
         o.beta2, o.weight_decay, o.grad_clip = HYPER["beta2"], HYPER["wd"], HYPER["clip"]
-        secs = []
+        secs, norms1 = [], []
         for i in range(2 + 4):
             hg.copy_(gsrc1)                       # the backward pass's output, untimed
             t0 = time.perf_counter()
             rc = L1.anni_lm_adam_step_scaled(opt, HYPER["lr"], 1.0)
             secs.append(time.perf_counter() - t0)
             assert rc == 0 and o.last_skipped == 0
+            # the step left every host gradient zeroed, and saw the same gradients as the first step
+            assert not bool(hg.any()), "host gradients not cleared by the step"
+            norms1.append(o.last_grad_norm)
+            assert abs(norms1[-1] - norms1[0]) <= 1e-9 * norms1[0]
         L1.anni_lm_adam_free(ctypes.byref(opt))
         sec = sum(secs[2:]) / len(secs[2:])
         e2e_c = {"value": n1 / sec, "unit": "params/s", "workload": "talk170m-fp32 (configuration 1)",
                  "n_params": n1, "ms_per_step": sec * 1e3, "h2d_bytes_per_step": 4 * n1,
                  "d2h_bytes_per_step": 48, "steps": len(secs) - 2,
                  "path": "anni_lm_adam_step_scaled: upload of pinned host fp32 gradients (147 tensors), "
-                         "one-launch step, status read, host gradients zeroed"}
+                         "one-launch step, status read, host gradients zeroed by a few threads behind the uploads"}
 
     driver_name = z.driver
     z.close()

@@ -51,6 +51,14 @@ extern "C" {
 ** reference's float in all but ~1e-7 of the elements, at about 7 % more time.
 */
 #define ANNI_STEP_EXACT_UPDATE	8
+/*
+** ZeRO-1 over peer memory, with a gradient arena named (anni_optstep_set_grad_arena) and
+** ANNI_STEP_ZERO_GRAD set: anni_optstep_reduce_norm[_range] clears this rank's own part of its
+** arena as it reads it (no other rank reads that part), and anni_optstep_update[_range] of the
+** same step, given the same flag, clears the other parts only.  Not with multicast reduction.
+** Both calls answer ANNI_E_ARG when the arena or the own part cannot be told from the peers.
+*/
+#define ANNI_STEP_REDUCE_CLEARS_OWN	16
 
 /* error codes (negative return values; also anni_optstep_status.error) */
 #define ANNI_OK			0

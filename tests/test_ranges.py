@@ -205,3 +205,54 @@ def test_rotated_peer_order_on_local_arenas():
         eng.close()
     for o in outs[1:]:
         assert o[0] == outs[0][0] and np.array_equal(o[1], outs[0][1]) and np.array_equal(o[2], outs[0][2])
+
+
+@pytest.mark.parametrize("gd", [DT_BF16, DT_F32])
+def test_reduce_clears_own_part_of_the_arena(gd):
+    """ANNI_STEP_REDUCE_CLEARS_OWN with two "ranks" on one GPU: the engine of rank 1 (the shorter
+    half) reads its shard out of both arenas; with the flag the reduce leaves rank 1's own part of
+    ITS arena zeroed (and touches nothing else), the update clears the rest of that arena and
+    leaves the other rank's alone; results equal the step without the flag.  The flag is refused
+    where no arena was named."""
+    from anni_b200.capi import STEP_REDUCE_CLEARS_OWN
+    tdt = torch.bfloat16 if gd == DT_BF16 else torch.float32
+    segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
+    n = segs.n
+    stride = -(-(-(-n // 2)) // 4096) * 4096
+    off, cnt = stride, n - stride
+    p, g, m, v = make_inputs(n, seed=11, grad_dtype=gd, state_dtype=DT_F32)
+    half = (to_dev(g).float() * 0.5).to(tdt)               # both ranks hold g/2: the sum is g exactly
+    outs = []
+    for flag in (0, STEP_REDUCE_CLEARS_OWN):
+        eng = OptStep(segs, grad_dtype=gd, state_dtype=DT_F32, shard_off=off, shard_n=cnt).allocate()
+        eng.master[:cnt].copy_(to_dev(p[off:]))
+        eng.m[:cnt].copy_(to_dev(m[off:]))
+        eng.v[:cnt].copy_(to_dev(v[off:]))
+        arenas = [torch.zeros(2 * stride, dtype=tdt, device="cuda") for _ in range(2)]
+        for a in arenas:
+            a[:n].copy_(half)
+        theirs = arenas[0].clone()
+        twins = [torch.zeros(2 * stride, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        eng.set_peers([a.data_ptr() for a in arenas], [t.data_ptr() for t in twins], None, off)
+        eng.rotate_peers(0)
+        hp = OptStep.hyper(lr=3e-4, t=3, beta2=0.95, wd=0.1, clip=1.0)
+        hp.flags |= flag
+        if flag:
+            with pytest.raises(AnniError):
+                eng.reduce_norm(hp)                             # no arena named yet
+        eng.set_grad_arena(arenas[1], stride, 2)
+        eng.reduce_norm(hp)
+        own = arenas[1]
+        assert torch.equal(arenas[0], theirs)
+        assert torch.equal(own[:stride], theirs[:stride])       # the part another rank reads: untouched
+        assert bool(own[stride:stride + cnt].any()) == (flag == 0)
+        eng.update(hp)
+        st = eng.status()
+        assert st.error == 0 and st.skipped == 0
+        assert not bool(own.any()) and torch.equal(arenas[0], theirs)
+        outs.append([st.norm] + [to_host(x[:cnt]).copy() for x in (eng.master, eng.m, eng.v, eng.grad)]
+                    + [to_host(twins[0][off:off + cnt]).copy()])
+        eng.close()
+    assert outs[0][0] == outs[1][0]
+    for a, b in zip(outs[0][1:], outs[1][1:]):
+        assert np.array_equal(a, b)
