@@ -469,8 +469,7 @@ class Zero1:
         if self.peer:
             if not grads_complete:
                 self._barrier()
-            if (not self.uses_multicast and self._arena_by_engine and (hp.flags & STEP_ZERO_GRAD)
-                    and os.environ.get("ANNI_B200_REDUCE_CLEARS_OWN", "1") != "0"):
+            if self.reduce_clears_own and (hp.flags & STEP_ZERO_GRAD):
                 # nobody else reads this rank's own part of its arena: the reduce clears it
                 own = type(hp).from_buffer_copy(hp)
                 own.flags |= STEP_REDUCE_CLEARS_OWN
@@ -553,6 +552,15 @@ class Zero1:
         mark("update+all_gather")
         self._barrier()
         mark("barrier")
+
+    @property
+    def reduce_clears_own(self):
+        """Peer-memory form without multicast: the reduce kernel clears this rank's own part of its
+        gradient arena as it reads it, and the update clears the other parts only
+        (ANNI_STEP_REDUCE_CLEARS_OWN; ``ANNI_B200_REDUCE_CLEARS_OWN=0`` turns it off)."""
+        return bool(self.world > 1 and self.peer and not self.copy_mode and not self.uses_multicast
+                    and getattr(self, "_arena_by_engine", False)
+                    and os.environ.get("ANNI_B200_REDUCE_CLEARS_OWN", "1") != "0")
 
     @property
     def driver(self):

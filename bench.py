@@ -420,7 +420,7 @@ def zero1_parity_check(dev, rank, world, zero1_kwargs):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from anni_b200.capi import DT_BF16
+    from anni_b200.capi import DT_BF16, STEP_REDUCE_CLEARS_OWN
     from anni_b200.engine import LM_SHAPES, OptStep, kernel_launches, lm_segments
     from anni_b200.zero1 import Zero1
 
@@ -552,10 +552,15 @@ def run_ours(args):
     wall1 = time.time()
     launches = kernel_launches() - launches0
     st = z.status()
+    phases_by_rank = None
     if world > 1:
         tmax = torch.tensor([total_ms], dtype=torch.float64, device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         total_ms = float(tmax.item())
+        # every rank's own view of the phases (a rank that waits for a slower one shows it in the
+        # phase that ends with an exchange)
+        phases_by_rank = [None] * world
+        dist.all_gather_object(phases_by_rank, {k: round(v / K, 4) for k, v in phase_ms.items()})
     ms_per_step = total_ms / K
     value = n / (ms_per_step * 1e-3)
     if args.profile:
@@ -653,7 +658,10 @@ def run_ours(args):
         for i in range(2 + 5):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            z.eng.update_range(hyper(t), 0, z.shard_n, first=True, last=True, local_twins=True)
+            hp_i = hyper(t)
+            if getattr(z, "reduce_clears_own", False):
+                hp_i.flags |= STEP_REDUCE_CLEARS_OWN         # as in the step: the reduce has cleared that part
+            z.eng.update_range(hp_i, 0, z.shard_n, first=True, last=True, local_twins=True)
             b.record()
             t += 1
             evs.append((a, b))
@@ -842,6 +850,7 @@ def run_ours(args):
         line["sustained"] = sustained
     if world > 1:
         line["phases_ms"] = {k: v / K for k, v in phase_ms.items()}
+        line["phases_ms_by_rank"] = phases_by_rank
         if hbm_only_ms is not None:
             line["phases_ms"]["update_hbm_only"] = hbm_only_ms
             line["per_rank_update"] = {
@@ -850,8 +859,9 @@ def run_ours(args):
                 "ms_without_arena_zeroing": hbm_nozero_ms,
                 "roofline_frac_without_arena_zeroing": alg_bytes * shard_n / (hbm_nozero_ms * 1e-3) / 1e9 / peak,
                 "note": "this rank's update on local memory alone (twins stored locally): the part of the step "
-                        "that shrinks with N; clearing the rank's full gradient arena (2 bytes per parameter of "
-                        "the WHOLE model on every rank) does not, hence the second figure"}
+                        "that shrinks with N; clearing the other ranks' parts of this rank's gradient arena (2 bytes "
+                        "per parameter of (N-1)/N of the WHOLE model; the own part is cleared by the reduce) "
+                        "does not, hence the second figure"}
         wire = (world - 1) / world * n * 2 / 1e9            # GB each way per GPU, per collective
         rs_ms = line["phases_ms"].get("reduce_scatter+norm", line["phases_ms"].get("reduce_scatter"))
         ag_ms = line["phases_ms"].get("update+all_gather", line["phases_ms"].get("all_gather"))
