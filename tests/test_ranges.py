@@ -207,13 +207,15 @@ def test_rotated_peer_order_on_local_arenas():
         assert o[0] == outs[0][0] and np.array_equal(o[1], outs[0][1]) and np.array_equal(o[2], outs[0][2])
 
 
+@pytest.mark.parametrize("ranged", [False, True], ids=["whole", "parts"])
 @pytest.mark.parametrize("gd", [DT_BF16, DT_F32])
-def test_reduce_clears_own_part_of_the_arena(gd):
+def test_reduce_clears_own_part_of_the_arena(gd, ranged):
     """ANNI_STEP_REDUCE_CLEARS_OWN with two "ranks" on one GPU: the engine of rank 1 (the shorter
     half) reads its shard out of both arenas; with the flag the reduce leaves rank 1's own part of
     ITS arena zeroed (and touches nothing else), the update clears the rest of that arena and
-    leaves the other rank's alone; results equal the step without the flag.  The flag is refused
-    where no arena was named."""
+    leaves the other rank's alone; results equal the step without the flag, also when both kernels
+    run part by part (the parts of the own part already reduced are zero, the others not yet).
+    The flag is refused where no arena was named."""
     from anni_b200.capi import STEP_REDUCE_CLEARS_OWN
     tdt = torch.bfloat16 if gd == DT_BF16 else torch.float32
     segs = lm_segments(**LM_SHAPES["tiny"], wd="matrices")
@@ -241,12 +243,23 @@ def test_reduce_clears_own_part_of_the_arena(gd):
             with pytest.raises(AnniError):
                 eng.reduce_norm(hp)                             # no arena named yet
         eng.set_grad_arena(arenas[1], stride, 2)
-        eng.reduce_norm(hp)
         own = arenas[1]
+        cuts = [(o, (cnt - o) if ln is None else ln) for o, ln in PARTS] if ranged else [(0, cnt)]
+        for i, (o, ln) in enumerate(cuts):
+            if ranged:
+                eng.reduce_norm_range(hp, o, ln, accumulate=i > 0)
+                if flag and i == 0:
+                    assert not bool(own[stride:stride + ln].any()) and bool(own[stride + ln:stride + cnt].any())
+            else:
+                eng.reduce_norm(hp)
         assert torch.equal(arenas[0], theirs)
         assert torch.equal(own[:stride], theirs[:stride])       # the part another rank reads: untouched
         assert bool(own[stride:stride + cnt].any()) == (flag == 0)
-        eng.update(hp)
+        for i, (o, ln) in enumerate(cuts):
+            if ranged:
+                eng.update_range(hp, o, ln, first=i == 0, last=i == len(cuts) - 1, local_twins=False)
+            else:
+                eng.update(hp)
         st = eng.status()
         assert st.error == 0 and st.skipped == 0
         assert not bool(own.any()) and torch.equal(arenas[0], theirs)
