@@ -217,3 +217,22 @@ def test_shard_geometry_properties():
             covered += c.value
         assert covered == n
     check()
+
+
+def test_binding_constants_equal_the_header():
+    """The Python binding's flag and type constants are the header's (a drifted copy would pass
+    wrong flags silently)."""
+    import re
+    from anni_b200 import capi
+    text = open(os.path.join(ROOT, "include", "anni_b200.h")).read()
+    text += open(os.path.join(ROOT, "include", "anni_zero1.h")).read()
+    defs = {m.group(1): int(m.group(2), 0)
+            for m in re.finditer(r"^#define\s+(ANNI_[A-Z0-9_]+)\s+\(?(-?(?:0x[0-9a-fA-F]+|\d+))u?\)?\s", text, re.M)}
+    pairs = {"ANNI_STEP_CHECK_FINITE": capi.STEP_CHECK_FINITE, "ANNI_STEP_ZERO_GRAD": capi.STEP_ZERO_GRAD,
+             "ANNI_STEP_DEV_LOSS_SCALE": capi.STEP_DEV_LOSS_SCALE, "ANNI_STEP_EXACT_UPDATE": capi.STEP_EXACT_UPDATE,
+             "ANNI_STEP_REDUCE_CLEARS_OWN": capi.STEP_REDUCE_CLEARS_OWN, "ANNI_DT_F32": capi.DT_F32,
+             "ANNI_DT_BF16": capi.DT_BF16, "ANNI_SEG_WD": capi.SEG_WD, "ANNI_SEG_TWIN_BF16": capi.SEG_TWIN_BF16,
+             "ANNI_SEG_TWIN_FP8": capi.SEG_TWIN_FP8, "ANNI_ZERO1_GRADS_COMPLETE": capi.ZERO1_GRADS_COMPLETE,
+             "ANNI_ZERO1_UNIQUE_ID_BYTES": capi.ZERO1_UNIQUE_ID_BYTES}
+    for name, value in pairs.items():
+        assert defs.get(name) == value, (name, defs.get(name), value)
