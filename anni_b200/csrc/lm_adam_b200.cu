@@ -12,7 +12,9 @@
 #include <stdlib.h>
 #include <string.h>
 #include <atomic>
+#include <chrono>
 #include <thread>
+#include <vector>
 #include "anni_gpu_compat.h"
 #include "anni_lm_adam.h"
 #include "optstep_internal.h"
@@ -556,65 +558,119 @@ extern "C" int anni_lm_adam_sync_host(anni_lm_adam *opt)
 /* ---- the step ----------------------------------------------------------------------- */
 
 /*
-** Clears the host gradient arrays (seg_scatter, lm_adam.c:413 of the reference).  With a
-** model's worth of them (hundreds of megabytes when every gradient lives on the host) one core
-** needs tens of milliseconds, so the tensors are dealt out to a few threads, and a tensor is
-** cleared as soon as ITS upload has returned, beside the uploads of the later ones: the step
-** then costs the longer of the two instead of their sum.  Small totals are cleared in place
-** after the launch.
+** Uploads the host gradient arrays and clears them (seg_gather / seg_scatter, lm_adam.c:361-413
+** of the reference).  With a model's worth of them (hundreds of megabytes when every gradient
+** lives on the host) one core needs tens of milliseconds for the clearing alone, so the arrays
+** are cut into pieces of at most 1 Mi elements, dealt out to a few threads, and a piece is
+** cleared as soon as ITS upload is through, beside the uploads of the later ones: the step then
+** costs the longer of the two instead of their sum, and what is left after the last upload is
+** one piece per thread.  Pinned fp32 gradients go up with asynchronous copies, back to back on
+** the default stream, an event behind each piece telling the threads when its source may
+** change; anything else with blocking copies.  Small totals are cleared in place after the
+** launch.
 */
 struct grad_clearer {
+	struct piece {
+		float	*src;
+		int64_t	n;
+		int64_t	off;	/* element offset in the gradient flat */
+	};
+	static const int64_t	PIECE = (int64_t)1 << 20;
+
 	anni_lm_adam		*opt = nullptr;
-	std::atomic<int>	ready{0};	/* tensors [0, ready) have been uploaded */
+	std::vector<piece>	pieces;
+	std::vector<cudaEvent_t> ev;		/* async: one per piece */
+	std::atomic<int>	ready{0};	/* pieces [0, ready) have been handed to the copy */
 	std::atomic<int>	stop{0};
-	std::thread		th[8];
+	std::thread		th[16];
 	int			n_th = 0;
+	bool			async = false;
+	int			device = 0;
 
-	static int64_t host_elems(const anni_lm_adam *o)
+	static bool pinned(const void *p)
 	{
-		int64_t total = 0;
+		cudaPointerAttributes at;
 
-		for (int i = 0; i < o->n_segs; i++)
-			if (o->segs[i].dw)
-				total += o->segs[i].n;
-		return total;
+		if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+			(void)cudaGetLastError();
+			return false;
+		}
+		return at.type == cudaMemoryTypeHost;
 	}
 	void start(anni_lm_adam *o)
 	{
 		const unsigned hw = std::thread::hardware_concurrency();
+		int64_t total = 0;
 
 		opt = o;
-		if (host_elems(o) < ((int64_t)32 << 20))
-			return;			/* cleared by clear_now() after the launch */
-		n_th = hw >= 16 ? 8 : hw >= 8 ? 4 : 2;
+		for (int i = 0; i < o->n_segs; i++) {
+			const anni_lm_adam_seg *sg = &o->segs[i];
+
+			if (!sg->dw)
+				continue;
+			total += sg->n;
+			for (int64_t at = 0; at < sg->n; at += PIECE)
+				pieces.push_back({ sg->dw + at, sg->n - at < PIECE ? sg->n - at : PIECE, sg->off + at });
+		}
+		if (total < ((int64_t)32 << 20))
+			return;			/* cleared by finish() after the launch */
+		n_th = hw >= 16 ? 12 : hw >= 8 ? 6 : 2;	/* the caller's own thread only queues copies and waits */
+		async = o->grad_dtype == ANNI_DT_F32 && cudaGetDevice(&device) == cudaSuccess;
+		for (int i = 0; async && i < o->n_segs; i++)
+			if (o->segs[i].dw && o->segs[i].n > 0 && !pinned(o->segs[i].dw))
+				async = false;
+		if (async) {
+			ev.assign(pieces.size(), nullptr);
+			for (size_t k = 0; k < pieces.size(); k++)
+				if (cudaEventCreateWithFlags(&ev[k], cudaEventDisableTiming) != cudaSuccess) {
+					ev[k] = nullptr;
+					async = false;	/* the events made so far go with the object */
+					break;
+				}
+		}
 		for (int k = 0; k < n_th; k++)
 			th[k] = std::thread([this, k]() {
-				for (int i = k; i < opt->n_segs; i += n_th) {
-					if (!opt->segs[i].dw)
-						continue;
-					while (ready.load(std::memory_order_acquire) <= i) {
+				if (async)
+					(void)cudaSetDevice(device);
+				for (size_t i = (size_t)k; i < pieces.size(); i += (size_t)n_th) {
+					while (ready.load(std::memory_order_acquire) <= (int)i) {
 						if (stop.load(std::memory_order_relaxed))
 							return;
 						std::this_thread::yield();
 					}
-					memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
+					if (async && cudaEventSynchronize(ev[i]) != cudaSuccess)
+						return;		/* the step reports the error; the gradients stay */
+					memset(pieces[i].src, 0, (size_t)pieces[i].n * sizeof(float));
 				}
 			});
 	}
-	void uploaded(int i)
+	/* every piece to the device, in order; 0 or -1 */
+	int upload_all()
 	{
-		ready.store(i + 1, std::memory_order_release);
+		const size_t esz = elem_size(opt->grad_dtype);
+
+		for (size_t i = 0; i < pieces.size(); i++) {
+			const piece &pc = pieces[i];
+			void *dst = (char *)opt->d_grad + (size_t)pc.off * esz;
+
+			if (!async) {
+				if (upload_as(dst, opt->grad_dtype, pc.src, pc.n) != 0)
+					return -1;
+			} else if (cudaMemcpyAsync(dst, pc.src, (size_t)pc.n * sizeof(float), cudaMemcpyHostToDevice, 0)
+			    != cudaSuccess || cudaEventRecord(ev[i], 0) != cudaSuccess)
+				return -1;
+			ready.store((int)i + 1, std::memory_order_release);
+		}
+		return 0;
 	}
 	/* after the launch: waits for the threads, or clears small totals here */
 	void finish()
 	{
 		if (!opt)
 			return;
-		if (n_th == 0) {
-			for (int i = 0; i < opt->n_segs; i++)
-				if (opt->segs[i].dw)
-					memset(opt->segs[i].dw, 0, (size_t)opt->segs[i].n * sizeof(float));
-		}
+		if (n_th == 0)
+			for (const piece &pc : pieces)
+				memset(pc.src, 0, (size_t)pc.n * sizeof(float));
 		join();
 		opt = nullptr;
 	}
@@ -629,8 +685,28 @@ struct grad_clearer {
 	{
 		stop.store(1, std::memory_order_relaxed);
 		join();
+		for (cudaEvent_t e : ev)
+			if (e)
+				(void)cudaEventDestroy(e);
 	}
 };
+
+static double now_us(void)
+{
+	return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+static int step_trace(void)
+{
+	static int on = -1;
+
+	if (on < 0) {
+		const char *e = getenv("ANNI_B200_STEP_TRACE");
+
+		on = e && atoi(e) != 0;
+	}
+	return on;
+}
 
 /* ANN_GNORM_EVERY=k: report the gradient norm every k-th step (adam_gnorm_every, lm_adam.c:438-450) */
 static int gnorm_every(void)
@@ -657,6 +733,7 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	anni_optstep_hyper hp;
 	anni_optstep_status st;
 	grad_clearer clearer;
+	double t_mark[5] = { now_us(), 0.0, 0.0, 0.0, 0.0 };
 	int host_grads = 0;
 	int rc;
 	int i;
@@ -671,23 +748,20 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	for (i = 0; i < opt->n_segs; i++)
 		if (opt->segs[i].dw)
 			host_grads = 1;
+	t_mark[1] = now_us();
 	if (host_grads) {		/* seg_gather (lm_adam.c:361-396) for host-resident gradients */
 		if (!opt->d_grad) {
 			rc = ANNI_E_ARG;
 			goto fail;
 		}
 		clearer.start(opt);
-		for (i = 0; i < opt->n_segs; i++) {
-			const anni_lm_adam_seg *s = &opt->segs[i];
-
-			if (s->dw && upload_as((char *)opt->d_grad + (size_t)s->off * elem_size(opt->grad_dtype),
-			    opt->grad_dtype, s->dw, s->n) != 0) {
-				rc = ANNI_E_CUDA;
-				goto fail;
-			}
-			clearer.uploaded(i);	/* the copy has returned: the source may change */
+		t_mark[1] = now_us();
+		if (clearer.upload_all() != 0) {
+			rc = ANNI_E_CUDA;
+			goto fail;
 		}
 	}
+	t_mark[2] = now_us();
 	memset(&hp, 0, sizeof(hp));
 	hp.lr = lr;
 	hp.beta1 = opt->beta1;
@@ -706,8 +780,14 @@ extern "C" int anni_lm_adam_step_scaled(anni_lm_adam *opt, double lr, double gra
 	rc = anni_optstep_step(opt->engine, &hp, NULL);
 	if (rc != ANNI_OK)
 		goto fail;
+	t_mark[3] = now_us();
 	clearer.finish();		/* the host gradient vectors are zero from here on (lm_adam.c:413) */
+	t_mark[4] = now_us();
 	rc = anni_optstep_status_read(opt->engine, &st, NULL);
+	if (step_trace())		/* ANNI_B200_STEP_TRACE=1: where the host side of a step spends its time */
+		fprintf(stderr, "[adam] step %d host us: prepare %.0f, uploads queued %.0f, launch %.0f, "
+		    "clearing waited %.0f, status %.0f\n", opt->t, t_mark[1] - t_mark[0], t_mark[2] - t_mark[1],
+		    t_mark[3] - t_mark[2], t_mark[4] - t_mark[3], now_us() - t_mark[4]);
 	if (rc == ANNI_OK && st.error != 0)
 		rc = st.error;
 	if (rc != ANNI_OK)

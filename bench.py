@@ -795,7 +795,7 @@ def run_ours(args):
                  "n_params": n1, "ms_per_step": sec * 1e3, "h2d_bytes_per_step": 4 * n1,
                  "d2h_bytes_per_step": 48, "steps": len(secs) - 2,
                  "path": "anni_lm_adam_step_scaled: upload of pinned host fp32 gradients (147 tensors), "
-                         "one-launch step, status read, host gradients zeroed by a few threads behind the uploads"}
+                         "one-launch step, status read, host gradients cleared piece by piece by a few threads behind asynchronous uploads"}
 
     driver_name = z.driver
     z.close()

@@ -359,6 +359,38 @@ def test_optimizer_object_semantics(oracle):
     assert (np.abs(p.astype(np.float64) - rp) <= 2 * np.spacing(np.abs(rp)) + 2e-9).all()
 
 
+def test_large_host_gradients_are_uploaded_and_cleared():
+    """A model's worth of host gradients (98 M fp32: above the size from which the step deals the
+    clearing out to threads behind the uploads; pinned arrays go up with asynchronous copies and
+    an event per tensor, pageable ones with blocking copies): two steps see exactly the gradients
+    they were given -- the norm is that of the arrays, the same on both steps -- leave every host
+    gradient zero, and give the same weights whichever way the gradients travelled."""
+    L = _mirror()
+    segs = lm_segments(**LM_SHAPES["blocks3"], wd="matrices")
+    n = segs.n
+    gen = torch.Generator().manual_seed(77)
+    p0 = torch.empty(n).normal_(0, 0.02, generator=gen)
+    g_src = torch.empty(n).normal_(0, 1e-3, generator=gen)
+    want = float(torch.linalg.vector_norm(g_src.double()))
+    results = []
+    for pinned in (True, False):
+        p_t = p0.clone()
+        g_t = torch.empty(n, pin_memory=pinned)
+        p, g = p_t.numpy(), g_t.numpy()
+        opt = _make_opt(L, segs, p, g)
+        o = opt.contents
+        o.grad_clip, o.weight_decay = 1.0, 0.1
+        for _ in range(2):
+            g_t.copy_(g_src)
+            assert L.anni_lm_adam_step(opt, 3e-4) == 0 and o.last_skipped == 0
+            assert abs(o.last_grad_norm - want) <= 1e-9 * want
+            assert not bool(g_t.any())
+        assert L.anni_lm_adam_sync_host(opt) == 0
+        results.append(p.copy())
+        L.anni_lm_adam_free(C.byref(opt))
+    assert np.array_equal(results[0], results[1]) and not np.array_equal(results[0], p0.numpy())
+
+
 def test_resume_from_reference_format_checkpoint_and_save_back(oracle, tmp_path):
     """A checkpoint in the reference's format (tied-embedding kind, BPE table embedded) is loaded
     into the optimizer object, two steps run on the GPU, the result is saved in the same format;
