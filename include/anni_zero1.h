@@ -12,10 +12,11 @@
 **   peer mode (the caller handed in peer-accessible pointers of every rank's arenas, e.g. from
 **   CUDA IPC or symmetric memory):
 **     [all-reduce of one float: every rank's gradients are complete]
-**     reduce-scatter + norm kernel   reads this shard out of every rank's gradient arena
+**     reduce-scatter + norm kernel   reads this shard out of every rank's gradient arena and
+**                                    clears the part of this rank's arena that only it reads
 **     all-reduce(sum) of 2 doubles   global sum of squares and non-finite flag
 **     update kernel                  decision, AdamW, twins stored into every rank's twin arena,
-**                                    this rank's whole gradient arena cleared
+**                                    the rest of this rank's gradient arena cleared
 **     [all-reduce(max) of per-tensor amax; quantise kernel]       (e4m3 twins only)
 **     all-reduce of one float        every rank's twins have landed
 **   NCCL mode (no peer pointers):
